@@ -4,7 +4,7 @@ request holds.
 
 Paged groups: keys and values of all order items with the same
 (kv heads, head size, window), pool [items, pages, kv heads, page size, head
-size] each for K and V; one page id of a group means that page in every item
+size] each for K and V (K alone for a group whose rows are keys and values at once); one page id of a group means that page in every item
 of the group. The reference sizes one pool for all layers, convolution layers
 included (tools/infer/src/main.rs:386-392); here only items that keep keys
 have pages. State groups: [items, slots, *shape] for order items with
@@ -67,7 +67,7 @@ class CacheManager:
         for g, need in enumerate(self.paged_keys):
             shape = (members[("paged", g)], self.group_pages[g], need.num_kv_heads, self.page_size, need.head_dim)
             self.k_pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
-            self.v_pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
+            self.v_pools.append(torch.zeros(shape, dtype=dtype, device=self.device) if need.values else None)
         for g, need in enumerate(self.state_keys):
             self.states.append(torch.zeros((members[("state", g)], self.num_slots) + tuple(need.shape),
                                            dtype=need.dtype, device=self.device))
@@ -156,7 +156,7 @@ class CacheManager:
             fam, g, idx = ig
             if fam == "paged":
                 out.append(CacheBinding(need=self.paged_keys[g], writes=not self._borrowed[i],
-                                        k=self.k_pools[g][idx], v=self.v_pools[g][idx],
+                                        k=self.k_pools[g][idx], v=self.v_pools[g][idx] if self.v_pools[g] is not None else None,
                                         block_table=block_tables[g], page_size=self.page_size,
                                         num_pages=self.group_pages[g]))
             else:
@@ -167,4 +167,4 @@ class CacheManager:
     def bytes_per_token(self) -> int:
         """Bytes of keys and values one token occupies over all paged groups."""
         el = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * p.shape[0] * p.shape[2] * p.shape[4] * el for p in self.k_pools)
+        return sum((2 if v is not None else 1) * p.shape[0] * p.shape[2] * p.shape[4] * el for p, v in zip(self.k_pools, self.v_pools))

@@ -22,12 +22,14 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """A layer: an arrangement (`block`) of a mixer, a feed-forward and their norms."""
-    block: str
+    """A layer: an arrangement (`block`) of a mixer, a feed-forward and their norms. `block` is the arrangement's
+    registered kind, or a PartSpec when the arrangement has parameters and weights of its own (gates on the way into
+    the stream, for instance). A layer without a feed-forward has None for it and for its norm."""
+    block: Any
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: Optional[PartSpec]
 
 
 @dataclass(frozen=True)

@@ -35,7 +35,9 @@ def _effective_model_type(d: dict):
 
 
 def resolve_architecture(d: dict) -> str:
-    archs = d.get("architectures") or []
+    archs = list(d.get("architectures") or [])
+    if isinstance(d.get("architecture"), str):        # some designs name themselves with one string
+        archs.append(d["architecture"])
     for a in archs:
         if a in _ARCHITECTURES:
             return a

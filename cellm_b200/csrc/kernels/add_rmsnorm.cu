@@ -2,6 +2,7 @@
 //
 //   all rows:       x[t] += delta[t];  y[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w
 //   selected rows:  v = x[rows[r]] + delta[rows[r]];  y[r] = v / sqrt(mean(v^2) + eps) * w
+//   groups > 1:     the mean is taken over each of `groups` equal consecutive parts of the row by itself
 //
 // The residual stream x is 32-bit in every mode; sum and norm are 32-bit
 // (crates/cellm-kernels/src/cpu_kernels.rs:17-34 is the formula: the weight is
@@ -13,7 +14,7 @@
 template <typename TA, typename TW>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ delta,
                                    const TW* __restrict__ w, TA* __restrict__ y,
-                                   const int* __restrict__ rows, int H, float eps) {
+                                   const int* __restrict__ rows, int H, int groups, float eps) {
     __shared__ float scratch[32];
     pdl_trigger();
     pdl_wait();
@@ -22,20 +23,25 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
     float* xr = x + (size_t)t * H;
     const TA* dr = delta ? delta + (size_t)t * H : nullptr;
     const bool write_back = (rows == nullptr) && (delta != nullptr);
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = xr[i];
-        if (dr) v += to_float(dr[i]);
-        if (write_back) xr[i] = v;
-        ss += v * v;
-    }
-    ss = block_sum(ss, scratch);
-    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
     TA* yr = y + (size_t)r * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = xr[i];
-        if (dr && !write_back) v += to_float(dr[i]);
-        yr[i] = from_float<TA>(v * inv * to_float(w[i]));
+    // groups > 1: the row in equal consecutive parts, each divided by its own root mean square
+    const int Hg = H / groups;
+    for (int g = 0; g < groups; ++g) {
+        const int lo = g * Hg, hi = lo + Hg;
+        float ss = 0.f;
+        for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+            float v = xr[i];
+            if (dr) v += to_float(dr[i]);
+            if (write_back) xr[i] = v;
+            ss += v * v;
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)Hg + eps);
+        for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+            float v = xr[i];
+            if (dr && !write_back) v += to_float(dr[i]);
+            yr[i] = from_float<TA>(v * inv * to_float(w[i]));
+        }
     }
 }
 
@@ -99,10 +105,11 @@ __global__ void add_rmsnorm_vec8_kernel(float* __restrict__ x, const __nv_bfloat
 // x: [*, H] float; delta: [*, H] act dtype or null; w: [H]; y: [n_rows, H] act dtype;
 // rows: null (all n_rows rows, x updated in place) or n_rows row indices (x left as is).
 CELLM_API int cellm_add_rmsnorm(float* x, const void* delta, const void* w, int w_dtype, void* y,
-                                const int* rows, int n_rows, int H, float eps, int act_dtype,
+                                const int* rows, int n_rows, int H, int groups, float eps, int act_dtype,
                                 cudaStream_t stream) {
     if (n_rows <= 0) return CELLM_OK;
-    if (act_dtype == CELLM_BF16 && (H & 7) == 0 && H <= 8192 && (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)y) & 15) == 0) {
+    if (groups < 1 || H % groups) return CELLM_ERR_SIZE;
+    if (groups == 1 && act_dtype == CELLM_BF16 && (H & 7) == 0 && H <= 8192 && (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)y) & 15) == 0) {
         const int vthreads = ((H / 8 + 31) / 32) * 32;
         if (w_dtype == CELLM_BF16)
             CELLM_RUN(add_rmsnorm_vec8_kernel<__nv_bfloat16>, n_rows, vthreads, 0, stream, x, (const __nv_bfloat16*)delta,
@@ -115,7 +122,7 @@ CELLM_API int cellm_add_rmsnorm(float* x, const void* delta, const void* w, int 
     }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
 #define LAUNCH(TA, TW) \
-    CELLM_RUN((add_rmsnorm_kernel<TA, TW>), n_rows, threads, 0, stream, x, (const TA*)delta, (const TW*)w, (TA*)y, rows, H, eps)
+    CELLM_RUN((add_rmsnorm_kernel<TA, TW>), n_rows, threads, 0, stream, x, (const TA*)delta, (const TW*)w, (TA*)y, rows, H, groups, eps)
     if (act_dtype == CELLM_F32 && w_dtype == CELLM_F32) LAUNCH(float, float);
     else if (act_dtype == CELLM_F32 && w_dtype == CELLM_BF16) LAUNCH(float, __nv_bfloat16);
     else if (act_dtype == CELLM_BF16 && w_dtype == CELLM_F32) LAUNCH(__nv_bfloat16, float);

@@ -14,14 +14,14 @@
 #include "common.cuh"
 
 #define ATTN_PLAIN_THREADS 128
-#define ATTN_PLAIN_MAX_HD 512
+#define ATTN_PLAIN_MAX_HD 1024
 
 template <typename TA>
 __global__ void __launch_bounds__(ATTN_PLAIN_THREADS)
 attention_plain_kernel(TA* __restrict__ out, const TA* __restrict__ q, const TA* __restrict__ k_pool,
                        const TA* __restrict__ v_pool, const int* __restrict__ positions,
                        const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
-                       int bt_stride, int num_pages, int page_size, int nh, int nkv, int hd, float scale,
+                       int bt_stride, int num_pages, int page_size, int nh, int nkv, int hd, int hdv, float scale,
                        int window, int* __restrict__ err) {
     constexpr int CH = ATTN_PLAIN_THREADS;
     extern __shared__ float smem[];
@@ -82,7 +82,7 @@ attention_plain_kernel(TA* __restrict__ out, const TA* __restrict__ q, const TA*
 #pragma unroll
         for (int r = 0; r < ATTN_PLAIN_MAX_HD / CH; ++r) {
             const int d = threadIdx.x + r * CH;
-            if (d < hd) {
+            if (d < hdv) {
                 float a = acc[r] * corr;
                 for (int jj = 0; jj < CH; ++jj) {
                     const int pgj = pg[jj];
@@ -98,31 +98,33 @@ attention_plain_kernel(TA* __restrict__ out, const TA* __restrict__ q, const TA*
 #pragma unroll
     for (int r = 0; r < ATTN_PLAIN_MAX_HD / CH; ++r) {
         const int d = threadIdx.x + r * CH;
-        if (d < hd) out[(size_t)t * nh * hd + (size_t)h * hd + d] = from_float<TA>(acc[r] * inv);
+        if (d < hdv) out[(size_t)t * nh * hdv + (size_t)h * hdv + d] = from_float<TA>(acc[r] * inv);
     }
 }
 
-// out, q: [T, nh*hd]; pools: one layer's keys and values; positions[t] is the
+// q: [T, nh*hd]; out: [T, nh*hdv]; pools: one layer's keys and values; positions[t] is the
 // token's place in its request (keys 0..positions[t] are read; the token's own
-// key must already be in the cache).
+// key must already be in the cache). A value is the first hdv entries of its row of hd
+// (hdv = hd for ordinary attention); v_pool may be k_pool itself, for a cache whose
+// rows serve as keys and, in their first part, as values.
 CELLM_API int cellm_attention_plain(void* out, const void* q, const void* k_pool, const void* v_pool,
                                     const int* positions, const int* seq_of_token, const int* block_table,
                                     int bt_stride, int num_pages, int page_size, int T, int nh, int nkv,
-                                    int hd, float scale, int window, int dtype, int* err,
+                                    int hd, int hdv, float scale, int window, int dtype, int* err,
                                     cudaStream_t stream) {
     if (T <= 0) return CELLM_OK;
-    if (hd > ATTN_PLAIN_MAX_HD || hd <= 0 || nkv <= 0 || nh % nkv) return CELLM_ERR_SIZE;
+    if (hd > ATTN_PLAIN_MAX_HD || hd <= 0 || hdv <= 0 || hdv > hd || nkv <= 0 || nh % nkv) return CELLM_ERR_SIZE;
     const size_t smem = (size_t)(hd + 2 * ATTN_PLAIN_THREADS) * sizeof(float);
     const unsigned grid = (unsigned)T * (unsigned)nh;
     if (dtype == CELLM_F32)
         CELLM_RUN(attention_plain_kernel<float>, grid, ATTN_PLAIN_THREADS, smem, stream,
             (float*)out, (const float*)q, (const float*)k_pool, (const float*)v_pool, positions, seq_of_token,
-            block_table, bt_stride, num_pages, page_size, nh, nkv, hd, scale, window, err);
+            block_table, bt_stride, num_pages, page_size, nh, nkv, hd, hdv, scale, window, err);
     else if (dtype == CELLM_BF16)
         CELLM_RUN(attention_plain_kernel<__nv_bfloat16>, grid, ATTN_PLAIN_THREADS, smem, stream,
             (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
             (const __nv_bfloat16*)v_pool, positions, seq_of_token, block_table, bt_stride, num_pages,
-            page_size, nh, nkv, hd, scale, window, err);
+            page_size, nh, nkv, hd, hdv, scale, window, err);
     else return CELLM_ERR_DTYPE;
     return CELLM_OK;
 }

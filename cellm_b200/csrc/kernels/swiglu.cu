@@ -31,3 +31,68 @@ CELLM_API int cellm_swiglu(void* h, const void* gu, int T, int ff, int dtype, in
     else return CELLM_ERR_DTYPE;
     return CELLM_OK;
 }
+
+// The gated feed-forward's middle in its general form: h[t, j] = act(g + bg[j]) * (u + bu[j]) with g = gu[t, j],
+// u = gu[t, ff + j]; act is silu (0) or the tanh form of gelu (1): 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+// The biases may be absent. 32-bit math.
+template <typename T, typename TI, typename TW>
+__global__ void gated_act_kernel(T* __restrict__ h, const TI* __restrict__ gu, const TW* __restrict__ bg,
+                                 const TW* __restrict__ bu, int ff, int act, size_t n) {
+    pdl_trigger();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const size_t t = i / ff;
+    const int j = (int)(i - t * ff);
+    float g = to_float(gu[t * 2 * ff + j]);
+    float u = to_float(gu[t * 2 * ff + ff + j]);
+    if (bg) g += to_float(bg[j]);
+    if (bu) u += to_float(bu[j]);
+    float a;
+    if (act == 1) a = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    else a = g * (1.0f / (1.0f + expf(-g)));
+    h[i] = from_float<T>(a * u);
+}
+
+CELLM_API int cellm_gated_act(void* h, const void* gu, const void* bg, const void* bu, int w_dtype, int T, int ff, int act,
+                              int dtype, int gu_dtype, cudaStream_t stream) {
+    const size_t n = (size_t)T * ff;
+    if (n == 0) return CELLM_OK;
+    if (act != 0 && act != 1) return CELLM_ERR_ARG;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((n + threads - 1) / threads);
+#define LAUNCH(TT, TI, TW) \
+    CELLM_RUN((gated_act_kernel<TT, TI, TW>), blocks, threads, 0, stream, (TT*)h, (const TI*)gu, (const TW*)bg, (const TW*)bu, ff, act, n)
+    if (dtype == CELLM_F32 && gu_dtype == CELLM_F32 && w_dtype == CELLM_F32) LAUNCH(float, float, float);
+    else if (dtype == CELLM_F32 && gu_dtype == CELLM_F32 && w_dtype == CELLM_BF16) LAUNCH(float, float, __nv_bfloat16);
+    else if (dtype == CELLM_BF16 && gu_dtype == CELLM_F32 && w_dtype == CELLM_BF16) LAUNCH(__nv_bfloat16, float, __nv_bfloat16);
+    else if (dtype == CELLM_BF16 && gu_dtype == CELLM_F32 && w_dtype == CELLM_F32) LAUNCH(__nv_bfloat16, float, float);
+    else if (dtype == CELLM_BF16 && gu_dtype == CELLM_BF16 && w_dtype == CELLM_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+    else return CELLM_ERR_DTYPE;
+#undef LAUNCH
+    return CELLM_OK;
+}
+
+// out[t, i] = in[t, i] + b[i]: a product's 32-bit sums take their bias before they are rounded to the activations' type.
+template <typename T, typename TW>
+__global__ void bias_add_kernel(T* __restrict__ out, const float* __restrict__ in, const TW* __restrict__ b, int N, size_t n) {
+    pdl_trigger();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    out[i] = from_float<T>(in[i] + to_float(b[i % N]));
+}
+
+CELLM_API int cellm_bias_add(void* out, const float* in, const void* b, int w_dtype, int T, int N, int dtype, cudaStream_t stream) {
+    const size_t n = (size_t)T * N;
+    if (n == 0) return CELLM_OK;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+#define LAUNCH(TT, TW) CELLM_RUN((bias_add_kernel<TT, TW>), blocks, 256, 0, stream, (TT*)out, in, (const TW*)b, N, n)
+    if (dtype == CELLM_F32 && w_dtype == CELLM_F32) LAUNCH(float, float);
+    else if (dtype == CELLM_F32 && w_dtype == CELLM_BF16) LAUNCH(float, __nv_bfloat16);
+    else if (dtype == CELLM_BF16 && w_dtype == CELLM_F32) LAUNCH(__nv_bfloat16, float);
+    else if (dtype == CELLM_BF16 && w_dtype == CELLM_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else return CELLM_ERR_DTYPE;
+#undef LAUNCH
+    return CELLM_OK;
+}

@@ -302,6 +302,11 @@ API long long cellm_exec_sizeof(int which) {
         case 12: return sizeof(cellm::PythonParams);
         case 13: return sizeof(cellm::ExecOps);
         case 14: return sizeof(cellm::LinearParams);
+        case 15: return sizeof(cellm::ReadStreamParams);
+        case 16: return sizeof(cellm::GatedNormAddParams);
+        case 17: return sizeof(cellm::MinGruParams);
+        case 18: return sizeof(cellm::LatentAttentionParams);
+        case 19: return sizeof(cellm::GatedMlpParams);
         default: return -1;
     }
 }

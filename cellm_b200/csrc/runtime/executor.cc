@@ -11,8 +11,8 @@ namespace {
 // ---- signatures of the kernel libraries' entry points (P = pointer, I = int, L = long long, F = float)
 typedef void* P;
 typedef const void* CP;
-typedef int (*EmbedFn)(P out, CP table, int tag, CP ids, int T, int H, int V, P err, P stream);
-typedef int (*AddRmsnormFn)(P x, CP delta, CP w, int w_tag, P y, CP rows, int n, int H, float eps, int act_tag, P stream);
+typedef int (*EmbedFn)(P out, CP table, int tag, CP ids, int T, int H, int V, float scale, P err, P stream);
+typedef int (*AddRmsnormFn)(P x, CP delta, CP w, int w_tag, P y, CP rows, int n, int H, int groups, float eps, int act_tag, P stream);
 typedef int (*ResidualAddFn)(P x, CP delta, i64 n, int act_tag, P stream);
 typedef int (*SwigluFn)(P h, CP gu, int T, int ff, int tag, int gu_tag, P stream);
 typedef int (*ShortConvFn)(P y, CP bcx, CP w, CP bias, int w_tag, P state, i64 slot_stride, CP slot_ids, CP seq, CP cu, int T,
@@ -21,7 +21,7 @@ typedef int (*QkNormRopeFn)(P q, CP qkv, i64 row_stride, CP q_w, CP k_w, int w_t
                             int bt_stride, P kp, P vp, int num_pages, int page_size, int T, int nh, int nkv, int hd, int rot,
                             int interleaved, CP inv_freq, int act_tag, P err, P stream);
 typedef int (*AttentionPlainFn)(P out, CP q, CP kp, CP vp, CP positions, CP seq, CP bt, int bt_stride, int pages, int page_size,
-                                int T, int nh, int nkv, int hd, float scale, int window, int tag, P err, P stream);
+                                int T, int nh, int nkv, int hd, int hdv, float scale, int window, int tag, P err, P stream);
 typedef int (*GemmPlainFn)(P c, CP a, CP w, int M, int N, int K, i64 lda, i64 ldw, i64 ldc, int a_tag, int out_tag, P stream);
 typedef int (*AttentionDecodeFn)(P out, P part_o, P part_ml, P counters, CP q, CP kp, CP vp, CP cu, CP ctx, CP bt, int bt_stride,
                                  int B, int T, int pages, int page_size, int nh, int nkv, int hd, float scale, int window,
@@ -38,6 +38,17 @@ typedef int (*GemmConvFn)(P y, CP a, CP wt, int M, int Nt, int K, i64 lda, i64 l
 typedef int (*GemmRopeFn)(P q, CP a, CP w, int M, int K, i64 lda, i64 ldw, int bn, int split_k, CP q_w, CP k_w, float eps,
                           CP positions, CP bt, int bt_stride, P kp, P vp, int pages, int page_size, int nh, int nkv, CP inv_freq,
                           int w_is_static, P err, P stream);
+typedef int (*GatedNormAddFn)(P x, CP m, CP gate, CP gate_bias, CP w, int w_tag, P y, int T, int H, int groups, float eps, int act_tag,
+                              P stream);
+typedef int (*StreamCastFn)(P y, CP x, i64 n, int act_tag, P stream);
+typedef int (*MinGruScanFn)(P out, CP proj, i64 ld, int proj_tag, CP bz, CP bx, int w_tag, P state, i64 slot_stride, CP slot_ids, CP cu,
+                            int T, int B, int W, int n_slots, int act_tag, P err, P stream);
+typedef int (*LatentPrepFn)(P q_plain, P q_full, CP proj, i64 ld, int proj_tag, CP c_norm_w, int w_tag, float eps, CP positions, CP seq,
+                            CP bt, int bt_stride, P pool, int pages, int page_size, int T, int heads, int dim, int rot_dim, int rank,
+                            int rot, CP inv_freq, int act_tag, P err, P stream);
+typedef int (*HeadProductFn)(P out, i64 ldo, i64 out_hs, CP in, i64 ldi, i64 in_hs, CP w, int T, int heads, int N, int K, int tag, P stream);
+typedef int (*GatedActFn)(P h, CP gu, CP bg, CP bu, int w_tag, int T, int ff, int act, int tag, int gu_tag, P stream);
+typedef int (*BiasAddFn)(P out, CP in, CP b, int w_tag, int T, int N, int tag, P stream);
 
 
 struct KernelError : std::runtime_error {
@@ -83,6 +94,9 @@ struct Run {
     ExecRegs regs{};
     void* slot[2] = {nullptr, nullptr};
     int turn = 0;
+    // layers whose sublayers read the stream itself: the stream in the activations' type, and whether y holds it now
+    void* stream_copy = nullptr;
+    bool stream_in_y = false;
 
     ExecFn last_fn = FN_COUNT;
     template <typename F> F fn(ExecFn which) {
@@ -155,8 +169,10 @@ struct Run {
     // ---- registers -----------------------------------------------------------------------------------------------
     // a part's output becomes the addend that waits; one that waits already goes into the stream first
     void set_pending(const void* out) {
-        if (regs.pending)
+        if (regs.pending) {
             LAUNCH(fn<ResidualAddFn>(FN_RESIDUAL_ADD)(regs.x, regs.pending, s.T * p.H, (int)act, s.stream), "residual_add");
+            stream_in_y = false;
+        }
         regs.pending = out;
     }
     const void* input() const {
@@ -165,7 +181,9 @@ struct Run {
     }
 
     void embed(const EmbedParams& e) {
-        LAUNCH(fn<EmbedFn>(FN_EMBED)(regs.x, e.table, (int)e.dtype, s.ids, (int)s.T, (int)p.H, (int)p.V, s.err, s.stream), "embed");
+        LAUNCH(fn<EmbedFn>(FN_EMBED)(regs.x, e.table, (int)e.dtype, s.ids, (int)s.T, (int)p.H, (int)p.V, (float)e.scale, s.err, s.stream),
+           "embed");
+        stream_in_y = false;
     }
     void rms_norm(const RmsNormParams& n) {
         const bool rows = regs.phase == 2;
@@ -173,10 +191,11 @@ struct Run {
         const i64 count = rows ? s.R : s.T;
         void* y = arena.take(count * p.H * elt(act));
         LAUNCH(fn<AddRmsnormFn>(FN_ADD_RMSNORM)(regs.x, regs.pending, n.w, (int)n.dtype, y, rows ? s.rows : nullptr, (int)count, (int)p.H,
-                                            (float)n.eps, (int)act, s.stream),
+                                            (int)std::max<i64>(n.groups, 1), (float)n.eps, (int)act, s.stream),
            "add_rmsnorm");
         if (!rows) regs.pending = nullptr;      // with rows given the stream itself is not touched
         regs.y = y;
+        stream_in_y = false;
     }
     void head(const HeadParams& h) {
         if (regs.phase != 2) throw std::runtime_error("executor: the output product belongs to the epilogue");
@@ -186,10 +205,53 @@ struct Run {
     void python(const PythonParams& py) {
         if (dry) return;
         if (!p.python) throw std::runtime_error("executor: a Python part in a program without a callback");
+        stream_in_y = false;
         if (p.python(py.token, &regs) != 0) throw std::runtime_error("executor: a Python part raised");
     }
 
+    // y = the stream in the activations' type (the 32-bit stream itself when the activations are 32-bit)
+    void read_stream() {
+        if (stream_in_y) return;
+        if (regs.pending) {
+            LAUNCH(fn<ResidualAddFn>(FN_RESIDUAL_ADD)(regs.x, regs.pending, s.T * p.H, (int)act, s.stream), "residual_add");
+            regs.pending = nullptr;
+        }
+        arena.release();
+        if (act == EXEC_F32) {
+            regs.y = regs.x;
+        } else {
+            if (!stream_copy) {
+                stream_copy = arena.take(s.T * p.H * elt(act));
+                arena.keep();
+            }
+            LAUNCH(fn<StreamCastFn>(FN_STREAM_CAST)(stream_copy, regs.x, s.T * p.H, (int)act, s.stream), "stream_cast");
+            regs.y = stream_copy;
+        }
+        stream_in_y = true;
+    }
+    // the waiting result of a sublayer, gated by a product over the sublayer's input (still in y), normed in groups
+    // and added into the stream; y = the new stream
+    void gated_norm_add(const GatedNormAddParams& n) {
+        if (!regs.pending) throw std::runtime_error("executor: a gate and norm without a sublayer's result before them");
+        if (regs.phase != 1) throw std::runtime_error("executor: a gate and norm outside the layers");
+        const i64 T = s.T, H = p.H;
+        void* g = nullptr;
+        if (n.gate.w) g = linear(input(), n.gate, T, H, act);
+        // without a copy of the stream yet (no sublayer of this pass has read the stream so far) y is left to the next reader
+        void* y = act != EXEC_F32 ? stream_copy : nullptr;
+        LAUNCH(fn<GatedNormAddFn>(FN_GATED_NORM_ADD)(regs.x, regs.pending, g, n.gate_bias, n.w, (int)n.w_dtype, y, (int)T, (int)H,
+                                                 (int)std::max<i64>(n.groups, 1), (float)n.eps, (int)act, s.stream),
+           "gated_norm_add");
+        regs.pending = nullptr;
+        regs.y = act == EXEC_F32 ? regs.x : y;
+        stream_in_y = regs.y != nullptr;
+        arena.release();
+    }
+
     void feed_forward(const SwiGLUParams& L, const void* x, void* out);
+    void gated_mlp(const GatedMlpParams& L, const void* x, void* out);
+    void mingru(const MinGruParams& L, const ExecItem& it, const void* x, void* out);
+    void latent_attention(const LatentAttentionParams& L, const ExecItem& it, const void* x, void* out);
     void short_conv(const ShortConvParams& L, const ExecItem& it, const void* x, void* out);
     void attention(const AttentionParams& L, const ExecItem& it, const void* x, void* out);
     void* attend(const AttentionParams& L, const ExecItem& it, const void* q, void* o = nullptr);
@@ -206,6 +268,15 @@ struct Run {
                 attention(*static_cast<const AttentionParams*>(op.params), *it, in, out);
                 break;
             case OP_SWIGLU: feed_forward(*static_cast<const SwiGLUParams*>(op.params), in, out); break;
+            case OP_GATED_MLP: gated_mlp(*static_cast<const GatedMlpParams*>(op.params), in, out); break;
+            case OP_MINGRU:
+                if (!it) throw std::runtime_error("executor: a mixer outside the layers");
+                mingru(*static_cast<const MinGruParams*>(op.params), *it, in, out);
+                break;
+            case OP_LATENT_ATTENTION:
+                if (!it) throw std::runtime_error("executor: a mixer outside the layers");
+                latent_attention(*static_cast<const LatentAttentionParams*>(op.params), *it, in, out);
+                break;
             case OP_LINEAR: {
                 const LinearParams& l = *static_cast<const LinearParams*>(op.params);
                 product(out, in, l.w, s.T, l.lda, l.out_dtype);
@@ -227,7 +298,9 @@ struct Run {
             case OP_RMS_NORM: rms_norm(*static_cast<const RmsNormParams*>(op.params)); break;
             case OP_HEAD: head(*static_cast<const HeadParams*>(op.params)); break;
             case OP_PYTHON: python(*static_cast<const PythonParams*>(op.params)); break;
-            case OP_SHORT_CONV: case OP_ATTENTION: case OP_SWIGLU: {
+            case OP_READ_STREAM: read_stream(); break;
+            case OP_GATED_NORM_ADD: gated_norm_add(*static_cast<const GatedNormAddParams*>(op.params)); break;
+            case OP_SHORT_CONV: case OP_ATTENTION: case OP_SWIGLU: case OP_MINGRU: case OP_LATENT_ATTENTION: case OP_GATED_MLP: {
                 void* out = slot[turn];
                 produce(op, it, input(), out);
                 set_pending(out);
@@ -438,7 +511,7 @@ void* Run::attend(const AttentionParams& L, const ExecItem& it, const void* q, v
     }
     // 32-bit, other head sizes: one block per (token, head) over the block table
     LAUNCH(fn<AttentionPlainFn>(FN_ATTENTION_PLAIN)(o, q, it.k, it.v, s.positions, s.seq_of_token, it.block_table, (int)it.bt_stride,
-                                                (int)it.num_pages, (int)it.page_size, (int)T, (int)nh, (int)nkv, (int)hd, scale,
+                                                (int)it.num_pages, (int)it.page_size, (int)T, (int)nh, (int)nkv, (int)hd, (int)hd, scale,
                                                 (int)L.window, (int)act, s.err, s.stream),
        "attention_plain");
     return o;
@@ -474,6 +547,60 @@ void Run::attention(const AttentionParams& L, const ExecItem& it, const void* x,
     }
     void* o = attend(L, it, q);
     product(out, o, L.out_proj, T, nh * hd, act);
+}
+
+void Run::gated_mlp(const GatedMlpParams& L, const void* x, void* out) {
+    const i64 T = s.T, H = p.H;
+    // gate and up stay 32-bit until act(g) * u is formed; the way back takes its bias before it is rounded
+    void* gu = linear(x, L.gate_up, T, H, EXEC_F32);
+    void* h = arena.take(T * L.ff * elt(act));
+    LAUNCH(fn<GatedActFn>(FN_GATED_ACT)(h, gu, L.bg, L.bu, (int)L.b_dtype, (int)T, (int)L.ff, (int)L.act, (int)act, (int)EXEC_F32, s.stream),
+           "gated_act");
+    if (L.bd) {
+        void* sums = linear(h, L.down, T, L.ff, EXEC_F32);
+        LAUNCH(fn<BiasAddFn>(FN_BIAS_ADD)(out, sums, L.bd, (int)L.b_dtype, (int)T, (int)L.down.N, (int)act, s.stream), "bias_add");
+    } else {
+        product(out, h, L.down, T, L.ff, act);
+    }
+}
+
+void Run::mingru(const MinGruParams& L, const ExecItem& it, const void* x, void* out) {
+    const i64 T = s.T, H = p.H, W = L.width;
+    if (!it.state) throw std::runtime_error("executor: a recurrent mixer without a state slot");
+    // the three projections side by side in 32-bit: everything that enters the recurrence is formed from the sums
+    void* proj = linear(x, L.in_proj, T, H, EXEC_F32);
+    void* y = arena.take(T * W * elt(act));
+    LAUNCH(fn<MinGruScanFn>(FN_MINGRU_SCAN)(y, proj, 3 * W, (int)EXEC_F32, L.bz, L.bx, (int)L.b_dtype, it.state, it.slot_stride, s.slot_ids,
+                                        s.cu_seqlens, (int)T, (int)s.B, (int)W, (int)it.n_slots, (int)act, s.err, s.stream),
+           "mingru_scan");
+    product(out, y, L.out_proj, T, W, act);
+}
+
+void Run::latent_attention(const LatentAttentionParams& L, const ExecItem& it, const void* x, void* out) {
+    const i64 T = s.T, H = p.H, nh = L.heads, kw = L.rank + L.rot_dim, e = elt(act);
+    void* proj = linear(x, L.in_proj, T, H, EXEC_F32);
+    void* q_plain = arena.take(T * nh * L.dim * e);
+    void* q_full = arena.take(T * nh * kw * e);
+    LAUNCH(fn<LatentPrepFn>(FN_LATENT_PREP)(q_plain, q_full, proj, L.in_proj.N, (int)EXEC_F32, L.c_norm_w, (int)L.c_norm_dtype, (float)L.eps,
+                                        s.positions, s.seq_of_token, it.block_table, (int)it.bt_stride, it.writes ? it.k : nullptr,
+                                        (int)it.num_pages, (int)it.page_size, (int)T, (int)nh, (int)L.dim, (int)L.rot_dim, (int)L.rank,
+                                        (int)L.rot, L.inv_freq, (int)act, s.err, s.stream),
+           "latent_prep");
+    // a head's query against the cached rows: [K_h^T q_h | rotated part]
+    LAUNCH(fn<HeadProductFn>(FN_HEAD_PRODUCT)(q_full, nh * kw, kw, q_plain, nh * L.dim, L.dim, L.absorb_k, (int)T, (int)nh, (int)L.rank,
+                                          (int)L.dim, (int)act, s.stream),
+           "head_product");
+    // every head reads the same rows (one key/value head); a value is a row's first `rank` entries
+    void* o_lat = arena.take(T * nh * L.rank * e);
+    LAUNCH(fn<AttentionPlainFn>(FN_ATTENTION_PLAIN)(o_lat, q_full, it.k, it.k, s.positions, s.seq_of_token, it.block_table, (int)it.bt_stride,
+                                                (int)it.num_pages, (int)it.page_size, (int)T, (int)nh, 1, (int)kw, (int)L.rank,
+                                                (float)L.scale, 0, (int)act, s.err, s.stream),
+           "attention_plain");
+    void* o = arena.take(T * nh * L.vdim * e);
+    LAUNCH(fn<HeadProductFn>(FN_HEAD_PRODUCT)(o, nh * L.vdim, L.vdim, o_lat, nh * L.rank, L.rank, L.expand_v, (int)T, (int)nh, (int)L.vdim,
+                                          (int)L.rank, (int)act, s.stream),
+           "head_product");
+    product(out, o, L.out_proj, T, nh * L.vdim, act);
 }
 
 int walk(const ExecProgram& p, ExecStep& s, bool dry, i64* need) {

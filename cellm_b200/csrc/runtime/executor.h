@@ -50,7 +50,9 @@ struct ExecLinear {
 enum OpKind : i64 {
     OP_EMBED = 0, OP_RMS_NORM, OP_SHORT_CONV, OP_ATTENTION, OP_SWIGLU, OP_HEAD, OP_PYTHON,
     // pieces of the above by themselves, for exec_part only (the interpreter's kernel wrappers)
-    OP_LINEAR, OP_ATTEND, OP_KINDS
+    OP_LINEAR, OP_ATTEND,
+    // a layer whose sublayers read the stream itself and whose results join it through a gate and a norm
+    OP_READ_STREAM, OP_GATED_NORM_ADD, OP_MINGRU, OP_LATENT_ATTENTION, OP_GATED_MLP, OP_KINDS
 };
 
 struct ExecOp {
@@ -58,8 +60,8 @@ struct ExecOp {
     const void* params;     // the kind's parameter struct below
 };
 
-struct EmbedParams { const void* table; i64 dtype; };                  // x = table[ids]
-struct RmsNormParams { const void* w; i64 dtype; double eps; };        // x += pending; y = rms_norm(x) * w
+struct EmbedParams { const void* table; i64 dtype; double scale; };    // x = table[ids] * scale
+struct RmsNormParams { const void* w; i64 dtype; double eps; i64 groups; };   // x += pending; y = rms_norm(x) * w (the mean over each of `groups` parts)
 struct ShortConvParams {
     ExecLinear in_proj, out_proj;
     const void* in_proj_tiled; i64 tiled_rows;      // in_proj in tiles of 42 channels for the fused decode kernel (null: none)
@@ -81,6 +83,27 @@ struct LinearParams { ExecLinear w; i64 lda, out_dtype; };             // out [T
 // OP_ATTEND takes AttentionParams and reads only nh, nkv, hd, window and scale: out = attention of the queries `in`
 // [T, nh * hd] (normed, turned) over the item's pages.
 
+// y = x in the activations' element type (a pending addend goes into x first): the input of a sublayer that reads the
+// stream itself. Nothing is launched when y already holds x.
+struct ReadStreamParams { i64 reserved; };
+// x += group_rms_norm(pending * sigmoid(y . gate^T + gate_bias)) * w, then y = x: a sublayer's result joins the stream.
+// gate.w null: no gate. y is the sublayer's input when the record starts.
+struct GatedNormAddParams { ExecLinear gate; const void* gate_bias; const void* w; i64 w_dtype, groups; double eps; };
+// minGRU: in_proj stacks the rows of z, candidate and output gate ([3 * width, H]); the state is the item's slot [width].
+struct MinGruParams { ExecLinear in_proj, out_proj; const void* bz; const void* bx; i64 b_dtype, width; };
+// Latent attention: in_proj stacks the queries' rows (heads * (dim + rot_dim)), the latent's (rank) and the shared
+// rotated key part's (rot_dim). absorb_k: [heads, rank, dim] (a head's key matrix transposed), expand_v: [heads, vdim,
+// rank]. The item's pages hold rows of rank + rot_dim values.
+struct LatentAttentionParams {
+    ExecLinear in_proj, out_proj;
+    const void* absorb_k; const void* expand_v;
+    i64 heads, dim, rot_dim, vdim, rank; double scale;
+    const void* c_norm_w; i64 c_norm_dtype; double eps;
+    i64 rot; const void* inv_freq;
+};
+// down . (act(gate . y + bg) * (up . y + bu)) + bd; act 0 silu, 1 gelu (tanh form); the biases may be null.
+struct GatedMlpParams { ExecLinear gate_up, down; const void* bg; const void* bu; const void* bd; i64 b_dtype, ff, act; };
+
 struct ExecOps { i64 n; const ExecOp* ops; };
 
 // The registers as a Python part sees and changes them.
@@ -98,7 +121,8 @@ typedef i64 (*PythonOpFn)(i64 token, ExecRegs* regs);
 // Entry points of the kernel libraries, in the order of ExecProgram::fns.
 enum ExecFn {
     FN_EMBED, FN_ADD_RMSNORM, FN_RESIDUAL_ADD, FN_SWIGLU, FN_SHORT_CONV, FN_QK_NORM_ROPE, FN_ATTENTION_PLAIN, FN_GEMM_PLAIN,
-    FN_ATTENTION_DECODE, FN_ATTENTION_TC, FN_ATTENTION_FLASH, FN_GEMM_TCGEN05, FN_GEMM_CONV, FN_GEMM_ROPE, FN_COUNT
+    FN_ATTENTION_DECODE, FN_ATTENTION_TC, FN_ATTENTION_FLASH, FN_GEMM_TCGEN05, FN_GEMM_CONV, FN_GEMM_ROPE,
+    FN_GATED_NORM_ADD, FN_STREAM_CAST, FN_MINGRU_SCAN, FN_LATENT_PREP, FN_HEAD_PRODUCT, FN_GATED_ACT, FN_BIAS_ADD, FN_COUNT
 };
 
 struct ExecProgram {

@@ -36,15 +36,20 @@ class DecoderModel:
         self.mixer_classes = []
         for spec in plan.layers:
             mixer = _build("mixer", spec.mixer, tensors, dtype)
-            ffn = _build("feed_forward", spec.feed_forward, tensors, dtype)
+            ffn = _build("feed_forward", spec.feed_forward, tensors, dtype) if spec.feed_forward is not None else None
             n1 = _build("norm", spec.mixer_norm, tensors, dtype)
-            n2 = _build("norm", spec.feed_forward_norm, tensors, dtype)
-            self.blocks.append(part_class("block", spec.block)(n1, mixer, n2, ffn))
+            n2 = _build("norm", spec.feed_forward_norm, tensors, dtype) if spec.feed_forward_norm is not None else None
+            if isinstance(spec.block, PartSpec):      # an arrangement with parameters and weights of its own
+                self.blocks.append(part_class("block", spec.block.kind)(n1, mixer, n2, ffn, spec.block.params,
+                                                                        _weights_of(spec.block, tensors), dtype))
+            else:
+                self.blocks.append(part_class("block", spec.block)(n1, mixer, n2, ffn))
             self.mixer_classes.append(type(mixer))
         # a decode step may be captured in a CUDA graph only if every part says that its forward() just launches
         every = [self.embedding, self.head, self.final_norm]
         for b in self.blocks:
-            every += [b] + [getattr(b, n) for n in ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm") if hasattr(b, n)]
+            every += [b] + [getattr(b, n) for n in ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm")
+                            if getattr(b, n, None) is not None]
             position = getattr(getattr(b, "mixer", None), "position", None)
             if position is not None:
                 every.append(position)

@@ -18,14 +18,21 @@ _ERRORS = {-1: "unsupported element type", -2: "a size this kernel does not take
 
 _SIGNATURES = {
     "kernels_common": {
-        "cellm_embed": [P, P, I, P, I, I, I, P, P],
+        "cellm_embed": [P, P, I, P, I, I, I, F, P, P],
         "cellm_upload": [P, P, L, P],
-        "cellm_add_rmsnorm": [P, P, P, I, P, P, I, I, F, I, P],
+        "cellm_add_rmsnorm": [P, P, P, I, P, P, I, I, I, F, I, P],
         "cellm_residual_add": [P, P, L, I, P],
         "cellm_swiglu": [P, P, I, I, I, I, P],
         "cellm_short_conv": [P, P, P, P, I, P, L, P, P, P, I, I, I, I, I, I, I, P, P],
         "cellm_qk_norm_rope": [P, P, L, P, P, I, F, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, I, P, P],
-        "cellm_attention_plain": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P],
+        "cellm_attention_plain": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P],
+        "cellm_gated_norm_add": [P, P, P, P, P, I, P, I, I, I, F, I, P],
+        "cellm_stream_cast": [P, P, L, I, P],
+        "cellm_mingru_scan": [P, P, L, I, P, P, I, P, L, P, P, I, I, I, I, I, P, P],
+        "cellm_latent_prep": [P, P, P, L, I, P, I, F, P, P, P, I, P, I, I, I, I, I, I, I, I, P, I, P, P],
+        "cellm_head_product": [P, L, L, P, L, L, P, I, I, I, I, I, P],
+        "cellm_gated_act": [P, P, P, P, I, I, I, I, I, I, P],
+        "cellm_bias_add": [P, P, P, I, I, I, I, P],
         "cellm_argmax": [P, P, I, I, P, P],
         "cellm_take_pending_tokens": [P, P, P, P, I, I, P, P],
         "cellm_keep_last_tokens": [P, P, P, I, I, P],

@@ -9,20 +9,21 @@ from ._lib import check, count_launch, fn, ptr, require_cuda, stream_of, tag
 _LIB = "kernels_common"
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, err: torch.Tensor) -> torch.Tensor:
-    """Rows of `table` [V, H] for int32 ids [T] as float32 [T, H]."""
+def embed(table: torch.Tensor, ids: torch.Tensor, err: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """Rows of `table` [V, H] for int32 ids [T], times `scale`, as float32 [T, H]."""
     require_cuda(table, ids, err)
     T, (V, H) = ids.numel(), table.shape
     out = torch.empty((T, H), dtype=torch.float32, device=table.device)
-    check(fn(_LIB, "cellm_embed")(ptr(out), ptr(table), tag(table), ptr(ids), T, H, V, ptr(err),
+    check(fn(_LIB, "cellm_embed")(ptr(out), ptr(table), tag(table), ptr(ids), T, H, V, float(scale), ptr(err),
                                   stream_of(table)), "embed")
     return out
 
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, eps: float,
-                act_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+                act_dtype: torch.dtype, rows: Optional[torch.Tensor] = None, groups: int = 1) -> torch.Tensor:
     """x [*, H] float32 (+= delta in place when rows is None); returns the normed
-    rows in act_dtype: all of them, or those listed in `rows`."""
+    rows in act_dtype: all of them, or those listed in `rows`. `groups` > 1: each of that
+    many equal consecutive parts of a row is divided by its own root mean square."""
     require_cuda(x, delta, w, rows)
     H = x.shape[-1]
     if x.dtype != torch.float32 or w.numel() != H:
@@ -32,7 +33,7 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor,
     n = x.shape[0] if rows is None else rows.numel()
     y = torch.empty((n, H), dtype=act_dtype, device=x.device)
     check(fn(_LIB, "cellm_add_rmsnorm")(ptr(x), ptr(delta), ptr(w), tag(w), ptr(y), ptr(rows), n, H,
-                                        float(eps), tag(act_dtype), stream_of(x)), "add_rmsnorm")
+                                        int(groups), float(eps), tag(act_dtype), stream_of(x)), "add_rmsnorm")
     return y
 
 
@@ -118,18 +119,20 @@ def qk_norm_rope(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[t
 
 def attention_plain(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, positions: torch.Tensor,
                     seq_of_token: torch.Tensor, block_table: torch.Tensor, nh: int, scale: float,
-                    window: int, err: torch.Tensor) -> torch.Tensor:
+                    window: int, err: torch.Tensor, value_dim: Optional[int] = None) -> torch.Tensor:
     """q [T, nh*hd]; pools [pages, kv_heads, page_size, hd]; each token reads keys
-    0..positions[t] (or the last `window`) of its request."""
+    0..positions[t] (or the last `window`) of its request. `value_dim`: a value is the first
+    that many entries of its row (default hd); `v_pool` may then be `k_pool` itself."""
     require_cuda(q, k_pool, v_pool, positions, seq_of_token, block_table, err)
     pages, nkv, page_size, hd = k_pool.shape
     T = q.shape[0]
+    hdv = hd if value_dim is None else int(value_dim)
     if q.shape[1] != nh * hd or k_pool.dtype != q.dtype or v_pool.shape != k_pool.shape:
         raise ValueError("attention_plain: shapes or element types do not fit")
-    out = torch.empty_like(q)
+    out = torch.empty((T, nh * hdv), dtype=q.dtype, device=q.device)
     check(fn(_LIB, "cellm_attention_plain")(
         ptr(out), ptr(q), ptr(k_pool), ptr(v_pool), ptr(positions), ptr(seq_of_token), ptr(block_table),
-        block_table.stride(0), pages, page_size, T, nh, nkv, hd, float(scale), int(window), tag(q),
+        block_table.stride(0), pages, page_size, T, nh, nkv, hd, hdv, float(scale), int(window), tag(q),
         ptr(err), stream_of(q)), "attention_plain")
     return out
 
@@ -189,3 +192,74 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
                                    ptr(penalty), ptr(recent), W, int(max_top_k), ptr(group_max),
                                    stream_of(logits)), "sample")
     return out
+
+
+def stream_cast(x: torch.Tensor, act_dtype: torch.dtype) -> torch.Tensor:
+    """The 32-bit stream in the activations' element type (the stream itself when that is float32)."""
+    require_cuda(x)
+    if x.dtype != torch.float32:
+        raise ValueError("stream_cast: the stream is float32")
+    if act_dtype == torch.float32:
+        return x
+    y = torch.empty_like(x, dtype=act_dtype)
+    check(fn(_LIB, "cellm_stream_cast")(ptr(y), ptr(x), x.numel(), tag(act_dtype), stream_of(x)), "stream_cast")
+    return y
+
+
+def gated_norm_add(x: torch.Tensor, m: torch.Tensor, gate: Optional[torch.Tensor], gate_bias: Optional[torch.Tensor],
+                   w: torch.Tensor, groups: int, eps: float, want_copy: bool = True) -> Optional[torch.Tensor]:
+    """x [T, H] float32 += group_rms_norm(m * sigmoid(gate + gate_bias)) * w, in place (gate None: no gate). m and gate
+    are of the activations' type. Returns the new stream in that type (x itself for float32), or None if not wanted."""
+    require_cuda(x, m, gate, gate_bias, w)
+    T, H = x.shape
+    if x.dtype != torch.float32 or m.shape != x.shape or (gate is not None and (gate.shape != x.shape or gate.dtype != m.dtype)):
+        raise ValueError("gated_norm_add: x float32 [T, H]; m and gate [T, H] of one element type")
+    if w.numel() != H or (gate_bias is not None and (gate_bias.numel() != H or gate_bias.dtype != w.dtype)):
+        raise ValueError("gated_norm_add: w and gate_bias have H values of one element type")
+    y = torch.empty_like(m) if (want_copy and m.dtype != torch.float32) else None
+    check(fn(_LIB, "cellm_gated_norm_add")(ptr(x), ptr(m), ptr(gate), ptr(gate_bias), ptr(w), tag(w), ptr(y), T, H, int(groups),
+                                           float(eps), tag(m), stream_of(x)), "gated_norm_add")
+    return y if y is not None else (x if want_copy else None)
+
+
+def mingru_scan(proj: torch.Tensor, bz: Optional[torch.Tensor], bx: Optional[torch.Tensor], state: torch.Tensor,
+                slot_ids: torch.Tensor, cu_seqlens: torch.Tensor, act_dtype: torch.dtype, err: torch.Tensor) -> torch.Tensor:
+    """proj [T, 3W] = [z | candidate | output gate] pre-activations; state [slots, W] float32, read and updated in place.
+    Returns S_t * silu(gate) [T, W] in act_dtype."""
+    require_cuda(proj, bz, bx, state, slot_ids, cu_seqlens, err)
+    T, W3 = proj.shape
+    W = W3 // 3
+    if W * 3 != W3 or state.dtype != torch.float32 or state.shape[1] != W:
+        raise ValueError(f"mingru_scan: shapes do not fit (proj {tuple(proj.shape)}, state {tuple(state.shape)})")
+    wt = tag(bz) if bz is not None else tag(act_dtype)
+    out = torch.empty((T, W), dtype=act_dtype, device=proj.device)
+    check(fn(_LIB, "cellm_mingru_scan")(ptr(out), ptr(proj), proj.stride(0), tag(proj), ptr(bz), ptr(bx), wt, ptr(state), state.stride(0),
+                                        ptr(slot_ids), ptr(cu_seqlens), T, cu_seqlens.numel() - 1, W, state.shape[0], tag(act_dtype),
+                                        ptr(err), stream_of(proj)), "mingru_scan")
+    return out
+
+
+def head_product(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [T, heads, K] (any row pitch, head pitch K or more) times per-head matrices w [heads, N, K] -> [T, heads, N];
+    `out` may be a view with pitches of its own (last axis dense)."""
+    heads, N, K = w.shape
+    T = x.shape[0]
+    if out is None:
+        out = torch.empty((T, heads, N), dtype=x.dtype, device=x.device)
+    if x.stride(2) != 1 or out.stride(2) != 1 or x.dtype != w.dtype or out.dtype != w.dtype or not w.is_contiguous():
+        raise ValueError("head_product: dense last axes and one element type")
+    check(fn(_LIB, "cellm_head_product")(out.data_ptr(), out.stride(0), out.stride(1), x.data_ptr(), x.stride(0), x.stride(1),
+                                         ptr(w), T, heads, N, K, tag(w), stream_of(x)), "head_product")
+    return out
+
+
+def gated_act(gu: torch.Tensor, bg: Optional[torch.Tensor], bu: Optional[torch.Tensor], act: str,
+              out_dtype: torch.dtype) -> torch.Tensor:
+    """gu [T, 2 ff] = [gate | up] -> act(gate + bg) * (up + bu); act "silu" or "gelu_tanh"."""
+    require_cuda(gu, bg, bu)
+    T, two_ff = gu.shape
+    h = torch.empty((T, two_ff // 2), dtype=out_dtype, device=gu.device)
+    wt = tag(bg) if bg is not None else tag(out_dtype)
+    check(fn(_LIB, "cellm_gated_act")(ptr(h), ptr(gu), ptr(bg), ptr(bu), wt, T, two_ff // 2, {"silu": 0, "gelu_tanh": 1}[act],
+                                      tag(h), tag(gu), stream_of(gu)), "gated_act")
+    return h

@@ -40,10 +40,13 @@ class TensorSpec:
 @dataclass(frozen=True)
 class PagedKV:
     """Keys and values that grow with the sequence, kept in pages.
-    window = 0: all keys are kept; window = w: a token reads its last w keys."""
+    window = 0: all keys are kept; window = w: a token reads its last w keys.
+    values = False: the rows serve as keys and values at once (a compressed cache whose values are a part
+    of the key rows): only the pool of keys exists."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    values: bool = True
 
 
 @dataclass(frozen=True)
@@ -91,7 +94,7 @@ class CacheBinding:
     writes: bool = True                       # False: the item reads another item's cache
     # paged
     k: Optional[torch.Tensor] = None          # [pages, kv_heads, page_size, head_dim]
-    v: Optional[torch.Tensor] = None
+    v: Optional[torch.Tensor] = None          # None in a group without a pool of values
     block_table: Optional[torch.Tensor] = None  # [B, max_blocks] int32, -1 = no page
     page_size: int = 0
     num_pages: int = 0

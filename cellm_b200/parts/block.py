@@ -24,3 +24,91 @@ class PreNormBlock(Block):
 
 
 register_block("pre_norm", PreNormBlock)
+
+
+class GatedPostNormBlock(Block):
+    """A layer whose sublayers read the residual stream itself and whose norm sits on the sublayer's result:
+
+        x += norm1(mixer(x) * sigmoid(G1 x + g1));    x += norm2(feed_forward(x) * sigmoid(G2 x + g2))
+
+    The gates (`gate`: True) are the block's own weights; a layer without a feed-forward has the first line only. The
+    norms must be RMS norms (in groups or not): gate, norm and the sum into the stream are one kernel, which also
+    leaves the stream in the activations' type for the next sublayer's products.
+
+    params: hidden_size, gate (default False). weights: mixer_gate, feed_forward_gate [H, H] and mixer_gate_bias,
+    feed_forward_gate_bias [H] if gate (the feed-forward's only if the layer has one)."""
+    graph_safe = True
+
+    @classmethod
+    def weight_specs(cls, params):
+        from .base import TensorSpec
+        H = params["hidden_size"]
+        specs = {}
+        if params.get("gate"):
+            specs["mixer_gate"] = TensorSpec((H, H), "linear")
+            specs["mixer_gate_bias"] = TensorSpec((H,), "bias")
+            if params.get("feed_forward", True):
+                specs["feed_forward_gate"] = TensorSpec((H, H), "linear")
+                specs["feed_forward_gate_bias"] = TensorSpec((H,), "bias")
+        return specs
+
+    def __init__(self, mixer_norm, mixer, feed_forward_norm, feed_forward, params=None, weights=None, dtype=None):
+        from ..config.errors import ConfigError
+        from .linear import Linear
+        self.mixer_norm, self.mixer = mixer_norm, mixer
+        self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward
+        params, weights = params or {}, weights or {}
+        self.dtype = dtype
+        for n in (mixer_norm, feed_forward_norm):
+            if n is not None and not all(hasattr(n, a) for a in ("weight", "eps", "groups")):
+                raise ConfigError("gated_post_norm: the norms must be RMS norms (weight, eps, groups)")
+        self.gates = {}
+        if params.get("gate"):
+            for name in ("mixer", "feed_forward"):
+                if name + "_gate" in weights:
+                    self.gates[name] = (Linear(weights[name + "_gate"], dtype), weights[name + "_gate_bias"].contiguous())
+        self._keep = []
+
+    def _join(self, emitter, name: str, norm) -> None:
+        from ..ops._lib import tag
+        from ..runtime import records as R
+        p = R.GatedNormAddParams()
+        if name in self.gates:
+            lin, bias = self.gates[name]
+            if not emitter.fits(lin.weight):
+                from ..config.errors import ConfigError
+                raise ConfigError("gated_post_norm: a gate kept in another element type than the activations")
+            bias = bias.to(norm.weight.dtype).contiguous()      # the kernel reads bias and norm weight as one element type
+            self._keep.append(bias)
+            p.gate, p.gate_bias = R.linear(lin.weight), bias.data_ptr()
+        p.w, p.w_dtype, p.groups, p.eps = norm.weight.data_ptr(), tag(norm.weight), norm.groups, norm.eps
+        emitter.native(R.GATED_NORM_ADD, p, part=self)
+
+    def emit(self, emitter) -> None:
+        from ..runtime import records as R
+        emitter.native(R.READ_STREAM, R.ReadStreamParams(0), part=self)
+        self.mixer.emit(emitter)
+        self._join(emitter, "mixer", self.mixer_norm)
+        if self.feed_forward is not None:
+            self.feed_forward.emit(emitter)
+            self._join(emitter, "feed_forward", self.feed_forward_norm)
+
+    def _sublayer(self, residual: Residual, name: str, norm, run) -> None:
+        from .. import ops
+        x = residual.flush()
+        h = ops.stream_cast(x, self.dtype)
+        m = run(h)
+        g = b = None
+        if name in self.gates:
+            lin, b = self.gates[name]
+            g = lin(h)
+            b = b.to(norm.weight.dtype)
+        ops.gated_norm_add(x, m.to(self.dtype).contiguous(), g, b, norm.weight, norm.groups, norm.eps, want_copy=False)
+
+    def forward(self, residual: Residual, ctx: StepContext, cache: CacheBinding) -> None:
+        self._sublayer(residual, "mixer", self.mixer_norm, lambda h: self.mixer.forward(h, ctx, cache))
+        if self.feed_forward is not None:
+            self._sublayer(residual, "feed_forward", self.feed_forward_norm, lambda h: self.feed_forward.forward(h, ctx))
+
+
+register_block("gated_post_norm", GatedPostNormBlock)

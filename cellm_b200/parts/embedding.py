@@ -15,7 +15,7 @@ from .registry import register_embedding, register_head
 class TokenEmbedding(Embedding):
     graph_safe = True
 
-    """params: vocab_size, dim. weights: weight [vocab, dim]."""
+    """params: vocab_size, dim, scale (default 1: the row as it is). weights: weight [vocab, dim]."""
 
     @classmethod
     def weight_specs(cls, params):
@@ -23,14 +23,15 @@ class TokenEmbedding(Embedding):
 
     def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
         self.weight = weights["weight"].contiguous()
+        self.scale = float(params.get("scale", 1.0))
 
     def emit(self, emitter) -> None:
         from ..ops._lib import tag
         from ..runtime import records as R
-        emitter.native(R.EMBED, R.EmbedParams(self.weight.data_ptr(), tag(self.weight)), part=self)
+        emitter.native(R.EMBED, R.EmbedParams(self.weight.data_ptr(), tag(self.weight), self.scale), part=self)
 
     def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
-        return ops.embed(self.weight, token_ids, ctx.err)
+        return ops.embed(self.weight, token_ids, ctx.err, self.scale)
 
 
 class LinearHead(Head):

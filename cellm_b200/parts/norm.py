@@ -1,5 +1,6 @@
 """RMSNorm (crates/cellm-kernels/src/cpu_kernels.rs:17-34): x / sqrt(mean(x^2) + eps) * w,
-fused with the addition of whatever waits to be added to the residual stream."""
+fused with the addition of whatever waits to be added to the residual stream. With `groups` > 1 the
+vector is split into that many equal consecutive parts and each is divided by its own root mean square."""
 from __future__ import annotations
 
 from typing import Optional
@@ -7,6 +8,7 @@ from typing import Optional
 import torch
 
 from .. import ops
+from ..config.errors import ConfigError
 from .base import Norm, Residual, TensorSpec
 from .registry import register_norm
 
@@ -14,7 +16,7 @@ from .registry import register_norm
 class RMSNorm(Norm):
     graph_safe = True
 
-    """params: dim, eps. weights: weight [dim]."""
+    """params: dim, eps, groups (default 1). weights: weight [dim]."""
 
     @classmethod
     def weight_specs(cls, params):
@@ -23,17 +25,20 @@ class RMSNorm(Norm):
     def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
         self.dim = int(params["dim"])
         self.eps = float(params["eps"])
+        self.groups = int(params.get("groups", 1))
+        if self.groups < 1 or self.dim % self.groups:
+            raise ConfigError(f"rms_norm: {self.dim} values do not split into {self.groups} equal groups")
         self.weight = weights["weight"].contiguous()
         self.dtype = dtype
 
     def emit(self, emitter) -> None:
         from ..ops._lib import tag
         from ..runtime import records as R
-        emitter.native(R.RMS_NORM, R.RmsNormParams(self.weight.data_ptr(), tag(self.weight), self.eps), part=self)
+        emitter.native(R.RMS_NORM, R.RmsNormParams(self.weight.data_ptr(), tag(self.weight), self.eps, self.groups), part=self)
 
     def forward(self, residual: Residual, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         delta, residual.pending = residual.pending, None
-        y = ops.add_rmsnorm(residual.x, delta, self.weight, self.eps, self.dtype, rows)
+        y = ops.add_rmsnorm(residual.x, delta, self.weight, self.eps, self.dtype, rows, self.groups)
         if rows is not None and delta is not None:
             residual.pending = delta      # the stream itself was not updated
         return y

@@ -61,13 +61,17 @@ def plan_tiles(M: int, N: int, K: int, sms: int) -> tuple[int, int]:
     return int(out[0]), int(out[1])
 
 
-def entry_points(act_dtype: torch.dtype) -> list:
+def entry_points(act_dtype: torch.dtype, kinds=None) -> list:
     """Addresses of the compiled kernels' C symbols in the order of the executor's table; loads (and if need be
-    compiles) the libraries this element type calls into, and leaves the others' entries empty."""
+    compiles) the libraries this element type calls into, and leaves the others' entries empty. `kinds`: the record
+    kinds of the program (None: any); a library that only other kinds reach is left out as well."""
     from ..csrc import build as _build
     out = []
     for library, name in R.ENTRY_POINTS:
+        users = R.LIBRARY_USERS.get(library)
         if act_dtype == torch.float32 and library in R.BF16_ONLY_LIBRARIES:
+            out.append(None)
+        elif kinds is not None and users is not None and not any(k in kinds for k in users):
             out.append(None)
         else:
             out.append(ctypes.cast(getattr(_build.load(library), name), c_void_p).value)
@@ -142,7 +146,10 @@ class Program:
         p.layers, p.order = layer_arr, order_arr
         self._callback = R.PythonOpFn(self._python_op)
         p.python = self._callback
-        for i, addr in enumerate(entries if entries is not None else entry_points(self.dtype)):
+        kinds = None
+        if model is not None and self.all_native:
+            kinds = {r.kind for recs in [self.prologue, self.epilogue] + self.layers for r in recs}
+        for i, addr in enumerate(entries if entries is not None else entry_points(self.dtype, kinds)):
             p.fns[i] = addr
         self._keep += [a, b, per_layer, layer_arr, order_arr]
         self.program = p
@@ -177,7 +184,7 @@ class Program:
         for it, b in zip(items, bindings[:n_items]):
             it.writes = int(b.writes)
             if b.k is not None:
-                it.k, it.v, it.block_table = b.k.data_ptr(), b.v.data_ptr(), b.block_table.data_ptr()
+                it.k, it.v, it.block_table = b.k.data_ptr(), R.ptr(b.v), b.block_table.data_ptr()
                 it.bt_stride, it.num_pages, it.page_size = b.block_table.stride(0), b.k.shape[0], b.page_size
             if b.state is not None:
                 it.state = b.state.data_ptr() if b.state.numel() else None

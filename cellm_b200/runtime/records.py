@@ -19,7 +19,8 @@ from ..ops import _lib as klib
 I64, F64, PTR = c_longlong, c_double, c_void_p
 
 # record kinds, in the order of the executor's OpKind
-EMBED, RMS_NORM, SHORT_CONV, ATTENTION, SWIGLU, HEAD, PYTHON, LINEAR, ATTEND = range(9)
+(EMBED, RMS_NORM, SHORT_CONV, ATTENTION, SWIGLU, HEAD, PYTHON, LINEAR, ATTEND,
+ READ_STREAM, GATED_NORM_ADD, MINGRU, LATENT_ATTENTION, GATED_MLP) = range(14)
 
 
 class ExecLinear(Structure):
@@ -31,11 +32,11 @@ class ExecOp(Structure):
 
 
 class EmbedParams(Structure):
-    _fields_ = [("table", PTR), ("dtype", I64)]
+    _fields_ = [("table", PTR), ("dtype", I64), ("scale", F64)]
 
 
 class RmsNormParams(Structure):
-    _fields_ = [("w", PTR), ("dtype", I64), ("eps", F64)]
+    _fields_ = [("w", PTR), ("dtype", I64), ("eps", F64), ("groups", I64)]
 
 
 class ShortConvParams(Structure):
@@ -65,6 +66,29 @@ class LinearParams(Structure):
     _fields_ = [("w", ExecLinear), ("lda", I64), ("out_dtype", I64)]
 
 
+class ReadStreamParams(Structure):
+    _fields_ = [("reserved", I64)]
+
+
+class GatedNormAddParams(Structure):
+    _fields_ = [("gate", ExecLinear), ("gate_bias", PTR), ("w", PTR), ("w_dtype", I64), ("groups", I64), ("eps", F64)]
+
+
+class MinGruParams(Structure):
+    _fields_ = [("in_proj", ExecLinear), ("out_proj", ExecLinear), ("bz", PTR), ("bx", PTR), ("b_dtype", I64), ("width", I64)]
+
+
+class LatentAttentionParams(Structure):
+    _fields_ = [("in_proj", ExecLinear), ("out_proj", ExecLinear), ("absorb_k", PTR), ("expand_v", PTR),
+                ("heads", I64), ("dim", I64), ("rot_dim", I64), ("vdim", I64), ("rank", I64), ("scale", F64),
+                ("c_norm_w", PTR), ("c_norm_dtype", I64), ("eps", F64), ("rot", I64), ("inv_freq", PTR)]
+
+
+class GatedMlpParams(Structure):
+    _fields_ = [("gate_up", ExecLinear), ("down", ExecLinear), ("bg", PTR), ("bu", PTR), ("bd", PTR), ("b_dtype", I64),
+                ("ff", I64), ("act", I64)]
+
+
 class ExecOps(Structure):
     _fields_ = [("n", I64), ("ops", POINTER(ExecOp))]
 
@@ -81,9 +105,14 @@ ENTRY_POINTS = [("kernels_common", "cellm_embed"), ("kernels_common", "cellm_add
                 ("kernels_common", "cellm_attention_plain"), ("gemm_plain", "cellm_gemm_plain"),
                 ("attention_decode", "cellm_attention_decode"), ("attention_tc", "cellm_attention_tc"),
                 ("attention_flash", "cellm_attention_flash"), ("gemm_tcgen05", "cellm_gemm_tcgen05"),
-                ("gemm_tcgen05", "cellm_gemm_conv_tcgen05"), ("gemm_tcgen05", "cellm_gemm_rope_tcgen05")]
+                ("gemm_tcgen05", "cellm_gemm_conv_tcgen05"), ("gemm_tcgen05", "cellm_gemm_rope_tcgen05"),
+                ("kernels_common", "cellm_gated_norm_add"), ("kernels_common", "cellm_stream_cast"),
+                ("kernels_common", "cellm_mingru_scan"), ("kernels_common", "cellm_latent_prep"),
+                ("kernels_common", "cellm_head_product"), ("kernels_common", "cellm_gated_act"), ("kernels_common", "cellm_bias_add")]
 # libraries a model whose activations are 32-bit never calls into (they need not be compiled for it)
 BF16_ONLY_LIBRARIES = ("attention_decode", "attention_tc", "attention_flash", "gemm_tcgen05")
+# libraries that only records of these kinds reach (a program without such a record need not have them compiled)
+LIBRARY_USERS = {"attention_decode": (ATTENTION, ATTEND), "attention_tc": (ATTENTION, ATTEND), "attention_flash": (ATTENTION, ATTEND)}
 
 
 class ExecProgram(Structure):
@@ -110,7 +139,8 @@ class ExecStep(Structure):
 
 # in the order cellm_exec_sizeof() numbers them
 LAYOUT_CHECKED = (ExecLinear, ExecOp, ExecProgram, ExecItem, ExecStep, ExecRegs, EmbedParams, RmsNormParams, ShortConvParams,
-                  AttentionParams, SwiGLUParams, HeadParams, PythonParams, ExecOps, LinearParams)
+                  AttentionParams, SwiGLUParams, HeadParams, PythonParams, ExecOps, LinearParams, ReadStreamParams, GatedNormAddParams,
+                  MinGruParams, LatentAttentionParams, GatedMlpParams)
 
 
 def ptr(t: Optional[torch.Tensor]):

@@ -50,8 +50,12 @@ def expected_tensors(plan: ModelPlan) -> dict[str, TensorSpec]:
     for layer in plan.layers:
         _part_tensors("norm", layer.mixer_norm, out)
         _part_tensors("mixer", layer.mixer, out)
-        _part_tensors("norm", layer.feed_forward_norm, out)
-        _part_tensors("feed_forward", layer.feed_forward, out)
+        if layer.feed_forward_norm is not None:
+            _part_tensors("norm", layer.feed_forward_norm, out)
+        if layer.feed_forward is not None:
+            _part_tensors("feed_forward", layer.feed_forward, out)
+        if isinstance(layer.block, PartSpec):
+            _part_tensors("block", layer.block, out)
     return out
 
 

@@ -41,7 +41,7 @@ class Recorder:
         self._thunks = [ctypes.CFUNCTYPE(ctypes.c_int, *sigs[library][name])(stand_in(name, sigs[library][name]))
                         for library, name in records.ENTRY_POINTS]
         self.entries = [ctypes.cast(t, ctypes.c_void_p).value for t in self._thunks]
-        monkeypatch.setattr(program, "entry_points", lambda dtype: self.entries)
+        monkeypatch.setattr(program, "entry_points", lambda dtype, kinds=None: self.entries)
         monkeypatch.setattr(program, "sm_count", lambda device: sms)
         monkeypatch.setattr(program, "_BARE", {})
         monkeypatch.setattr(gemm_bf16, "_sms", lambda device: sms)

@@ -77,7 +77,7 @@ def test_attention_kernels():
     assert tc(hd=128) == SIZE and tc(ps=4) == SIZE and tc(scale=0.0) == SIZE and tc(q=A + 4) == ALIGN
 
     def plain(nh=4, nkv=2, hd=64):
-        return call("kernels_common", "cellm_attention_plain", A, A, A, A, A, A, A, 4, 8, 16, 2, nh, nkv, hd, 0.125, 0, 1, A, None)
+        return call("kernels_common", "cellm_attention_plain", A, A, A, A, A, A, A, 4, 8, 16, 2, nh, nkv, hd, hd, 0.125, 0, 1, A, None)
     assert plain(hd=520) == SIZE and plain(hd=0) == SIZE and plain(nh=5) == SIZE
 
 
