@@ -606,6 +606,7 @@ void Run::latent_attention(const LatentAttentionParams& L, const ExecItem& it, c
 int walk(const ExecProgram& p, ExecStep& s, bool dry, i64* need) {
     Run r{p, s, Arena{static_cast<char*>(s.arena), s.arena_bytes}, p.act_dtype};
     r.dry = r.arena.dry = dry;
+    if (dry) r.arena.base = reinterpret_cast<char*>(4096);     // sizes only: addresses that are never used, but not null
     const i64 T = s.T, H = p.H, e = elt(p.act_dtype);
     s.launches = 0;
     for (i64& c : s.calls) c = 0;
@@ -642,6 +643,7 @@ void exec_need(const ExecProgram& p, ExecStep& s, i64* need) { walk(p, s, true, 
 int exec_part(const ExecProgram& p, ExecStep& s, const ExecOp& op, const void* y_in, void* out, bool dry, i64* need) {
     Run r{p, s, Arena{static_cast<char*>(s.arena), s.arena_bytes}, p.act_dtype};
     r.dry = r.arena.dry = dry;
+    if (dry) r.arena.base = reinterpret_cast<char*>(4096);     // sizes only: addresses that are never used, but not null
     s.launches = 0;
     for (i64& c : s.calls) c = 0;
     if (s.T > 0) {
