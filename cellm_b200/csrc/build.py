@@ -40,6 +40,7 @@ LIBRARIES: dict[str, tuple[str, list[str], list[str]]] = {
     "attention_flash": ("nvcc", ["kernels/attention_flash.cu"], []),
     "attention_decode": ("nvcc", ["kernels/attention_decode.cu"], []),
     "attention_tc": ("nvcc", ["kernels/attention_tc.cu"], []),
+    "attention_latent": ("nvcc", ["kernels/attention_latent.cu"], []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -49,6 +49,8 @@ typedef int (*LatentPrepFn)(P q_plain, P q_full, CP proj, i64 ld, int proj_tag, 
 typedef int (*HeadProductFn)(P out, i64 ldo, i64 out_hs, CP in, i64 ldi, i64 in_hs, CP w, int T, int heads, int N, int K, int tag, P stream);
 typedef int (*GatedActFn)(P h, CP gu, CP bg, CP bu, int w_tag, int T, int ff, int act, int tag, int gu_tag, P stream);
 typedef int (*BiasAddFn)(P out, CP in, CP b, int w_tag, int T, int N, int tag, P stream);
+typedef int (*AttentionLatentFn)(P out, P part_o, P part_ml, CP q, CP pool, CP cu, CP ctx, CP bt, int bt_stride, int B, int T, int n_tiles,
+                                 int pages, int page_size, int nh, int kw, int dv, float scale, int nsplit, P err, P stream);
 
 
 struct KernelError : std::runtime_error {
@@ -592,6 +594,34 @@ void Run::latent_attention(const LatentAttentionParams& L, const ExecItem& it, c
            "head_product");
     // every head reads the same rows (one key/value head); a value is a row's first `rank` entries
     void* o_lat = arena.take(T * nh * L.rank * e);
+    // bfloat16 and sizes the tensor-core kernel takes (multiples of 16, value columns that split over its warps, tiles
+    // that fit shared memory): 64 (token, head) rows a CTA; the keys in pieces when the tiles alone leave SMs idle
+    i64 dvw = 0;
+    if (L.rank % 128 == 0 && L.rank / 128 <= 4) dvw = 128;
+    else if (L.rank % 64 == 0 && L.rank / 64 <= 4) dvw = 64;
+    else if (L.rank % 32 == 0 && L.rank / 32 <= 8) dvw = 32;
+    else if (L.rank % 16 == 0 && L.rank / 16 <= 8) dvw = 16;
+    const i64 bn = dvw == 64 ? 64 : 32;
+    if (p.latent_tc && act == EXEC_BF16 && L.scale > 0 && dvw && kw % 16 == 0 && (64 + 2 * bn) * (kw + 8) * 2 <= 227 * 1024) {
+        i64 n_tiles = 0;
+        for (i64 b = 0; b < s.B; ++b) n_tiles += ceil_div(s.q_lens[b] * nh, 64);
+        const i64 blocks = ceil_div(s.max_total_len, bn);
+        const i64 nsplit = std::max<i64>(1, std::min(ceil_div(2 * p.sms, n_tiles), blocks / 2));
+        void *part_o = nullptr, *part_ml = nullptr;
+        if (nsplit > 1) {
+            const i64 rows = T * nh;
+            need_attn_ws = std::max(need_attn_ws, nsplit * rows * (L.rank + 2));
+            if (!dry && nsplit * rows * (L.rank + 2) > s.attn_ws_floats) throw std::runtime_error("executor: the attention workspace is too small");
+            part_o = s.attn_ws;
+            part_ml = (float*)s.attn_ws + nsplit * rows * L.rank;
+        }
+        LAUNCH(fn<AttentionLatentFn>(FN_ATTENTION_LATENT)(o_lat, part_o, part_ml, q_full, it.k, s.cu_seqlens, s.ctx_lens, it.block_table,
+                                                      (int)it.bt_stride, (int)s.B, (int)T, (int)n_tiles, (int)it.num_pages,
+                                                      (int)it.page_size, (int)nh, (int)kw, (int)L.rank, (float)L.scale, (int)nsplit,
+                                                      s.err, s.stream),
+               "attention_latent");
+        if (nsplit > 1) ++launches;                    // the merge of the pieces
+    } else
     LAUNCH(fn<AttentionPlainFn>(FN_ATTENTION_PLAIN)(o_lat, q_full, it.k, it.k, s.positions, s.seq_of_token, it.block_table, (int)it.bt_stride,
                                                 (int)it.num_pages, (int)it.page_size, (int)T, (int)nh, 1, (int)kw, (int)L.rank,
                                                 (float)L.scale, 0, (int)act, s.err, s.stream),

@@ -122,13 +122,14 @@ typedef i64 (*PythonOpFn)(i64 token, ExecRegs* regs);
 enum ExecFn {
     FN_EMBED, FN_ADD_RMSNORM, FN_RESIDUAL_ADD, FN_SWIGLU, FN_SHORT_CONV, FN_QK_NORM_ROPE, FN_ATTENTION_PLAIN, FN_GEMM_PLAIN,
     FN_ATTENTION_DECODE, FN_ATTENTION_TC, FN_ATTENTION_FLASH, FN_GEMM_TCGEN05, FN_GEMM_CONV, FN_GEMM_ROPE,
-    FN_GATED_NORM_ADD, FN_STREAM_CAST, FN_MINGRU_SCAN, FN_LATENT_PREP, FN_HEAD_PRODUCT, FN_GATED_ACT, FN_BIAS_ADD, FN_COUNT
+    FN_GATED_NORM_ADD, FN_STREAM_CAST, FN_MINGRU_SCAN, FN_LATENT_PREP, FN_HEAD_PRODUCT, FN_GATED_ACT, FN_BIAS_ADD, FN_ATTENTION_LATENT, FN_COUNT
 };
 
 struct ExecProgram {
     i64 n_layers, n_order, H, V, act_dtype;
     i64 sms, static_flag, max_counters;
     i64 fused_conv, fused_rope;     // decode steps: in_proj + convolution, q/k/v product + norm + rotation as one kernel each
+    i64 latent_tc;                  // latent attention on the tensor cores where its sizes allow (0: the plain kernel always)
     i64 tc_min_ctas;                // prompt attention on tcgen05 from this many CTAs (< 0: an eighth of the SMs)
     double tc_min_fill;             // and this share of its tiles' rows in use
     ExecOps prologue, epilogue;

@@ -52,6 +52,10 @@ _SIGNATURES = {
         "cellm_attention_flash": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, P, P],
         "cellm_attention_flash_supports": [I],
     },
+    "attention_latent": {
+        "cellm_attention_latent": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
+        "cellm_attention_latent_supports": [I, I],
+    },
     "gemm_tcgen05": {
         "cellm_gemm_tcgen05": [P, P, P, I, I, I, L, L, L, I, I, I, I, I, P, P, P, P],
         "cellm_gemm_conv_tcgen05": [P, P, P, I, I, I, L, L, I, I, I, P, P, I, P, L, P, I, I, P, P],

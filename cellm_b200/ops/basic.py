@@ -263,3 +263,28 @@ def gated_act(gu: torch.Tensor, bg: Optional[torch.Tensor], bu: Optional[torch.T
     check(fn(_LIB, "cellm_gated_act")(ptr(h), ptr(gu), ptr(bg), ptr(bu), wt, T, two_ff // 2, {"silu": 0, "gelu_tanh": 1}[act],
                                       tag(h), tag(gu), stream_of(gu)), "gated_act")
     return h
+
+
+def attention_latent(q: torch.Tensor, pool: torch.Tensor, cu_seqlens: torch.Tensor, ctx_lens: torch.Tensor,
+                     block_table: torch.Tensor, q_lens, nh: int, dv: int, scale: float, nsplit: int,
+                     err: torch.Tensor) -> torch.Tensor:
+    """The tensor-core attention over a latent cache by itself: q [T, nh * kw] bfloat16, pool [pages, 1, page_size, kw];
+    every head reads the same rows, a value is a row's first dv entries. `q_lens`: the host's copy of the portions'
+    lengths; `nsplit`: pieces the keys are cut into. Returns [T, nh * dv]."""
+    require_cuda(q, pool, cu_seqlens, ctx_lens, block_table, err)
+    pages, one, page_size, kw = pool.shape
+    T = q.shape[0]
+    if one != 1 or q.shape[1] != nh * kw or q.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16:
+        raise ValueError("attention_latent: bfloat16 queries [T, nh * kw] over a pool [pages, 1, page_size, kw]")
+    n_tiles = sum((int(n) * nh + 63) // 64 for n in q_lens)
+    out = torch.empty((T, nh * dv), dtype=q.dtype, device=q.device)
+    part_o = part_ml = None
+    if nsplit > 1:
+        part_o = torch.empty((nsplit, T * nh, dv), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((nsplit, T * nh, 2), dtype=torch.float32, device=q.device)
+        count_launch()
+    check(fn("attention_latent", "cellm_attention_latent")(
+        ptr(out), ptr(part_o), ptr(part_ml), ptr(q), ptr(pool), ptr(cu_seqlens), ptr(ctx_lens), ptr(block_table),
+        block_table.stride(0), len(q_lens), T, n_tiles, pages, page_size, nh, kw, dv, float(scale), int(nsplit), ptr(err),
+        stream_of(q)), "attention_latent")
+    return out

@@ -28,7 +28,8 @@ from . import records as R
 # that serving reaches only at large sizes). fused_conv / fused_rope: decode steps run in_proj + short convolution,
 # and the q/k/v product + head norms + rotation + cache write, as one kernel each. attention_tc_*: prompt attention
 # goes to the tcgen05 kernel from this many CTAs (None: an eighth of the SMs) and this share of its tiles' rows in use.
-OPTIONS = {"fused_conv": True, "fused_rope": True, "attention_tc_min_ctas": None, "attention_tc_min_fill": 0.5}
+# latent_tc: latent attention runs on the tensor cores where its sizes allow (off: the plain kernel, as in 32-bit).
+OPTIONS = {"fused_conv": True, "fused_rope": True, "attention_tc_min_ctas": None, "attention_tc_min_fill": 0.5, "latent_tc": True}
 
 _bound = False
 
@@ -176,6 +177,7 @@ class Program:
     def _options(self) -> None:
         p = self.program
         p.fused_conv, p.fused_rope = int(OPTIONS["fused_conv"]), int(OPTIONS["fused_rope"])
+        p.latent_tc = int(OPTIONS["latent_tc"])
         p.tc_min_ctas = -1 if OPTIONS["attention_tc_min_ctas"] is None else int(OPTIONS["attention_tc_min_ctas"])
         p.tc_min_fill = float(OPTIONS["attention_tc_min_fill"])
 

@@ -108,17 +108,19 @@ ENTRY_POINTS = [("kernels_common", "cellm_embed"), ("kernels_common", "cellm_add
                 ("gemm_tcgen05", "cellm_gemm_conv_tcgen05"), ("gemm_tcgen05", "cellm_gemm_rope_tcgen05"),
                 ("kernels_common", "cellm_gated_norm_add"), ("kernels_common", "cellm_stream_cast"),
                 ("kernels_common", "cellm_mingru_scan"), ("kernels_common", "cellm_latent_prep"),
-                ("kernels_common", "cellm_head_product"), ("kernels_common", "cellm_gated_act"), ("kernels_common", "cellm_bias_add")]
+                ("kernels_common", "cellm_head_product"), ("kernels_common", "cellm_gated_act"), ("kernels_common", "cellm_bias_add"),
+                ("attention_latent", "cellm_attention_latent")]
 # libraries a model whose activations are 32-bit never calls into (they need not be compiled for it)
-BF16_ONLY_LIBRARIES = ("attention_decode", "attention_tc", "attention_flash", "gemm_tcgen05")
+BF16_ONLY_LIBRARIES = ("attention_decode", "attention_tc", "attention_flash", "gemm_tcgen05", "attention_latent")
 # libraries that only records of these kinds reach (a program without such a record need not have them compiled)
-LIBRARY_USERS = {"attention_decode": (ATTENTION, ATTEND), "attention_tc": (ATTENTION, ATTEND), "attention_flash": (ATTENTION, ATTEND)}
+LIBRARY_USERS = {"attention_decode": (ATTENTION, ATTEND), "attention_tc": (ATTENTION, ATTEND), "attention_flash": (ATTENTION, ATTEND),
+                 "attention_latent": (LATENT_ATTENTION,)}
 
 
 class ExecProgram(Structure):
     _fields_ = [("n_layers", I64), ("n_order", I64), ("H", I64), ("V", I64), ("act_dtype", I64),
                 ("sms", I64), ("static_flag", I64), ("max_counters", I64), ("fused_conv", I64), ("fused_rope", I64),
-                ("tc_min_ctas", I64), ("tc_min_fill", F64),
+                ("latent_tc", I64), ("tc_min_ctas", I64), ("tc_min_fill", F64),
                 ("prologue", ExecOps), ("epilogue", ExecOps), ("layers", POINTER(ExecOps)), ("order", POINTER(I64)),
                 ("python", PythonOpFn), ("fns", PTR * len(ENTRY_POINTS))]
 

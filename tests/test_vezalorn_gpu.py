@@ -359,3 +359,57 @@ def test_one_layer_alone(tmp_path, dtype, layer):
         got = run_trace(folder, dtype, FAMILIES[fam](reqs), 8)
         for rid, toks in reqs.items():
             check_close(traces.as_matrix(got[rid], len(toks)), plain.forward(cfg, w, toks).numpy(), dtype, f"{layer['type']} {fam} {rid}")
+
+
+@pytest.mark.parametrize("nh,kw,dv,page", [(8, 80, 64, 16), (16, 576, 512, 32), (5, 48, 32, 8), (3, 64, 48, 16), (2, 144, 128, 64)])
+def test_latent_attention_kernel_against_plain_kernel_and_torch(nh, kw, dv, page):
+    """The tensor-core kernel alone: portions of several requests at contexts that end inside a page and inside a block
+    of keys, whole and cut into pieces, against 64-bit torch over the same rounded inputs and the plain kernel."""
+    from cellm_b200 import ops
+    from cellm_b200.ops._state import error_word
+    g = torch.Generator().manual_seed(nh * 1000 + kw)
+    q_lens, ctx_lens = [70, 1, 9, 1], [131, 300, 0, 63]
+    B, T = len(q_lens), sum(q_lens)
+    width = max((c + n + page - 1) // page for c, n in zip(ctx_lens, q_lens))
+    n_pages = B * width + 3
+    order = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.full((B, width), -1, dtype=torch.int32)
+    for b in range(B):
+        for i in range((ctx_lens[b] + q_lens[b] + page - 1) // page):
+            table[b, i] = order.pop()
+    pool = (torch.randn(n_pages, 1, page, kw, generator=g) * 0.7).to(torch.bfloat16)
+    q = (torch.randn(T, nh * kw, generator=g) * 0.7).to(torch.bfloat16)
+    scale = 1.7 * kw ** -0.5
+    want = torch.zeros(T, nh, dv, dtype=torch.float64)
+    t = 0
+    for b in range(B):
+        total = ctx_lens[b] + q_lens[b]
+        keys = torch.stack([pool[table[b, j // page], 0, j % page] for j in range(total)]).double()
+        for i in range(q_lens[b]):
+            qi = q[t].double().reshape(nh, kw)
+            s = (qi @ keys[:ctx_lens[b] + i + 1].T) * scale
+            want[t] = torch.softmax(s, -1) @ keys[:ctx_lens[b] + i + 1, :dv]
+            t += 1
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    cu = i32([0] + list(np.cumsum(q_lens)))
+    err = error_word(torch.device(DEV))
+    positions = i32([c + j for c, n in zip(ctx_lens, q_lens) for j in range(n)])
+    seq = i32([b for b, n in enumerate(q_lens) for _ in range(n)])
+    poold, qd, tabled = pool.to(DEV), q.to(DEV), table.to(DEV)
+    plain_out = ops.attention_plain(qd, poold, poold, positions, seq, tabled, nh, scale, 0, err, value_dim=dv)
+    torch.testing.assert_close(plain_out.cpu().double().reshape(T, nh, dv), want, rtol=2e-2, atol=2e-2)
+    for nsplit in (1, 3, 8):
+        out = ops.attention_latent(qd, poold, cu, i32(ctx_lens), tabled, q_lens, nh, dv, scale, nsplit, err)
+        torch.testing.assert_close(out.cpu().double().reshape(T, nh, dv), want, rtol=2e-2, atol=2e-2)
+    assert int(err.item()) == 0
+
+
+def test_latent_attention_takes_the_tensor_core_kernel(models):
+    from cellm_b200.runtime import program
+    folder, reqs, ref = models["c"]
+    before = program.CALLS["cellm_attention_latent"]
+    run_trace(folder, "bfloat16", traces.whole({"r0": reqs["r0"]}), 16)
+    assert program.CALLS["cellm_attention_latent"] > before
+    before = program.CALLS["cellm_attention_latent"]
+    run_trace(folder, "float32", traces.whole({"r0": reqs["r0"]}), 16)
+    assert program.CALLS["cellm_attention_latent"] == before
