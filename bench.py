@@ -228,6 +228,76 @@ def profile_region(loaded, args, rng) -> int:
     return 0
 
 
+def matrix_bytes(model) -> int:
+    """Bytes of every weight matrix a decode step reads once (each layer's parts and gates, the output product)."""
+    import torch
+    seen, total = set(), 0
+
+    def scan(obj, depth=0):
+        nonlocal total
+        if isinstance(obj, torch.Tensor):
+            if obj.dim() >= 2 and obj.data_ptr() not in seen:
+                seen.add(obj.data_ptr())
+                total += obj.numel() * obj.element_size()
+        elif isinstance(obj, dict):
+            for v in obj.values():
+                scan(v, depth + 1)
+        elif isinstance(obj, (list, tuple)):
+            for v in obj:
+                scan(v, depth + 1)
+        elif depth < 4 and hasattr(obj, "__dict__"):
+            for k, v in vars(obj).items():
+                if k not in ("in_proj_tiled", "q_only", "_record", "_attend"):
+                    scan(v, depth + 1)
+    for blk in model.blocks:
+        scan(blk)
+    scan(model.head)
+    return total
+
+
+def compare_designs(args, rng) -> int:
+    """Prefill (one 2,048-token prompt) and decode (batch 8 and 1 after 2,048-token prompts) of the new design and of
+    LFM2 at equal sizes, device-timed with CUDA events through the step function."""
+    import torch
+    from cellm_b200 import write_random_model
+    from cellm_b200.config.presets import LFM2_SHAPES, VEZALORN_SHAPES
+    from cellm_b200.models import load_model
+    from cellm_b200.weights import InitSpec
+    pk, pk_src = peaks()
+    out = {}
+    for size in [s for s in args.sizes.split(",") if s]:
+        shape, like = VEZALORN_SHAPES[size]
+        row = {}
+        for name, config in ((args.design, shape), (like, LFM2_SHAPES[like])):
+            with tempfile.TemporaryDirectory(prefix="cellm_bench_") as d:
+                write_random_model(d, config, seed=0, dtype="bfloat16", init=InitSpec(norm_jitter=0.0))
+                loaded = load_model(d, "bfloat16", "cuda:0")
+            wbytes = matrix_bytes(loaded[2])
+            pf_ms = time_prefill(loaded, rng)
+            r = {"matrix_gb": round(wbytes / 1e9, 3), "prefill_ms": round(pf_ms, 3),
+                 "prefill_tok_s": round(PROMPT_LEN / (pf_ms * 1e-3), 1),
+                 "prefill_frac_of_bf16_peak": round(2 * PROMPT_LEN * (wbytes / 2) / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+            for b in (args.batch, 1):
+                eng, ids = decode_setup(loaded, b, b * CONTEXT_LEN // PAGE, rng)
+                ms, e2e_ms, launches, _, _, ctx = time_decode(eng, ids, args.steps, args.warmup, rng)
+                step_bytes = wbytes + b * (ctx - args.steps / 2) * eng.cache.bytes_per_token()
+                r[f"decode_b{b}"] = {"ms": round(ms, 4), "tok_s": round(b / (ms * 1e-3), 1), "e2e_ms": round(e2e_ms, 4),
+                                     "launches": int(launches),
+                                     "hbm_frac": round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+                for x in ids:
+                    eng.cancel(x)
+                del eng
+                torch.cuda.empty_cache()
+            row[name] = r
+            del loaded
+            torch.cuda.empty_cache()
+        out[size] = row
+    print(json.dumps({"metric": "prefill and decode of %s beside LFM2 at equal sizes" % args.design, "dtype": "bf16",
+                      "data": "synthetic: random token ids, random-init weights", "peaks": pk_src, "steps": args.steps,
+                      "warmup": args.warmup, "prompt_len": PROMPT_LEN, "sizes": out}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -236,6 +306,10 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 runs")
+    ap.add_argument("--design", default=None, choices=["vezalorn"],
+                    help="instead of the default workload: prefill and decode throughput of this design at a few sizes, "
+                         "beside LFM2 at equal width, depth and feed-forward (random weights); prints one JSON line")
+    ap.add_argument("--sizes", default="700m,1.2b", help="with --design: which of the shapes to run")
     ap.add_argument("--profile-region", choices=["decode", "prefill"], default=None,
                     help="for a profiler started with --profile-from-start off: run the set-up, then one eager "
                          "decode step (or one prefill) between cudaProfilerStart/Stop, print no bench line")
@@ -262,17 +336,23 @@ def main() -> int:
     rng = np.random.default_rng(0)
     pk, pk_src = peaks()
     t_setup = time.time()
+    config = LFM2_1P2B
+    if args.design:
+        if not args.profile_region:
+            return compare_designs(args, rng)
+        from cellm_b200.config.presets import VEZALORN_SHAPES
+        config = VEZALORN_SHAPES[args.sizes.split(",")[0]][0]          # a profiler's region on the new design's first size
     with tempfile.TemporaryDirectory(prefix="cellm_bench_") as d:
         # the benchmark's weights: N(0, 0.02), norm weights 1
-        write_random_model(d, LFM2_1P2B, seed=0, dtype="bfloat16", init=InitSpec(norm_jitter=0.0))
+        write_random_model(d, config, seed=0, dtype="bfloat16", init=InitSpec(norm_jitter=0.0))
         loaded = load_model(d, "bfloat16", "cuda:0")
     cfg, plan, model = loaded
-    n_layers = cfg.num_hidden_layers
+    n_layers = len(plan.layers)
     weight_bytes = 0
     seen = set()
     for blk in model.blocks:
         for part in (blk.mixer, blk.feed_forward):
-            for v in vars(part).values():
+            for v in (vars(part).values() if part is not None else ()):
                 w = getattr(v, "weight", None)
                 if isinstance(w, torch.Tensor) and w.data_ptr() not in seen:
                     seen.add(w.data_ptr())

@@ -31,3 +31,24 @@ def shape(name: str) -> dict:
         return dict(LFM2_SHAPES[name.lower()])
     except KeyError:
         raise ValueError(f"unknown shape {name!r}; known: {sorted(LFM2_SHAPES)}") from None
+
+
+# ---- Vezalorn shapes beside LFM2's ---------------------------------------------------------------------------------
+def _vezalorn(width: int, layers: int, attention_at, heads: int, ff: int, vocab: int = 65536) -> dict:
+    """Layers of a width and count that an LFM2 shape has: recurrent layers of the model's width where LFM2 has its
+    short convolutions, latent attention (heads of 128 + 64 rotated values, a latent of 512) where it has attention,
+    and the same feed-forward width after every layer."""
+    attn = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
+            "rot": {"base": 1000000.0, "dims": 64}}
+    mlp = {"kind": "dense", "ff": ff}
+    return {"architecture": "Vezalorn", "vocab": vocab, "width": width, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-5, "groups": 2},
+            "layers": [{"type": "latent_attention", "mixer": dict(attn), "mlp": dict(mlp)} if i in attention_at else
+                       {"type": "mingru", "mixer": {"width": width}, "mlp": dict(mlp)} for i in range(layers)]}
+
+
+# name -> (Vezalorn shape, the LFM2 shape of equal width, depth, feed-forward and attention places)
+VEZALORN_SHAPES = {
+    "1.2b": (_vezalorn(2048, 16, [2, 5, 8, 10, 12, 14], 16, 8192), "lfm2-1.2b"),
+    "700m": (_vezalorn(1536, 16, [2, 5, 8, 10, 12, 14], 12, 6912), "lfm2-700m"),
+}
