@@ -43,6 +43,78 @@ __global__ void gated_norm_add_kernel(float* __restrict__ x, const TA* __restric
     }
 }
 
+// The same for bfloat16 activations and weights when a group is a multiple of 8 values and at most 8 * 1024: one block
+// per (row, group), every thread keeps its 8 values in registers, each element is read once and written once in
+// 16-byte pieces. The group's sum is taken in an order that depends on its length only.
+__global__ void gated_norm_add_vec8_kernel(float* __restrict__ x, const __nv_bfloat16* __restrict__ m,
+                                           const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ gate_bias,
+                                           const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int H, int Hg,
+                                           float eps) {
+    __shared__ float scratch[32];
+    pdl_trigger();
+    const int i0 = threadIdx.x * 8;
+    const bool on = i0 < Hg;
+    const int col = blockIdx.y * Hg + i0;
+    const size_t at = (size_t)blockIdx.x * H + col;
+    float wv[8], bv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) wv[j] = bv[j] = 0.f;
+    if (on) {                                   // weights and bias are not the work of the kernel before this one
+        const uint4 wq = *reinterpret_cast<const uint4*>(w + col);
+        const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wq);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(wp[j]); wv[2 * j] = f.x; wv[2 * j + 1] = f.y; }
+        if (gate_bias) {
+            const uint4 bq = *reinterpret_cast<const uint4*>(gate_bias + col);
+            const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&bq);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(bp[j]); bv[2 * j] = f.x; bv[2 * j + 1] = f.y; }
+        }
+    }
+    pdl_wait();
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    if (on) {
+        const uint4 mq = *reinterpret_cast<const uint4*>(m + at);
+        const __nv_bfloat162* mp = reinterpret_cast<const __nv_bfloat162*>(&mq);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(mp[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
+        if (gate) {
+            const uint4 gq = *reinterpret_cast<const uint4*>(gate + at);
+            const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gq);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(gp[j]);
+                v[2 * j] *= 1.0f / (1.0f + expf(-(f.x + bv[2 * j])));
+                v[2 * j + 1] *= 1.0f / (1.0f + expf(-(f.y + bv[2 * j + 1])));
+            }
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)Hg + eps);
+    if (on) {
+        const float4 a = *reinterpret_cast<const float4*>(x + at), b = *reinterpret_cast<const float4*>(x + at + 4);
+        float xv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) xv[j] += v[j] * inv * wv[j];
+        *reinterpret_cast<float4*>(x + at) = make_float4(xv[0], xv[1], xv[2], xv[3]);
+        *reinterpret_cast<float4*>(x + at + 4) = make_float4(xv[4], xv[5], xv[6], xv[7]);
+        if (y) {
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 pk = __floats2bfloat162_rn(xv[2 * j], xv[2 * j + 1]);
+                o[j] = *reinterpret_cast<uint32_t*>(&pk);
+            }
+            *reinterpret_cast<uint4*>(y + at) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
 // x: [T, H] float, updated in place; m, gate: [T, H] of the activations' type (gate may be null); gate_bias, w: [H] of the
 // weights' type (gate_bias may be null); y: [T, H] of the activations' type or null.
 CELLM_API int cellm_gated_norm_add(float* x, const void* m, const void* gate, const void* gate_bias, const void* w, int w_dtype,
@@ -50,6 +122,14 @@ CELLM_API int cellm_gated_norm_add(float* x, const void* m, const void* gate, co
     if (T <= 0) return CELLM_OK;
     if (groups < 1 || H % groups || H <= 0) return CELLM_ERR_SIZE;
     if (!x || !m || !w) return CELLM_ERR_ARG;
+    const int Hg = H / groups;
+    if (act_dtype == CELLM_BF16 && w_dtype == CELLM_BF16 && (Hg & 7) == 0 && Hg <= 8192 &&
+        (((uintptr_t)x | (uintptr_t)m | (uintptr_t)gate | (uintptr_t)gate_bias | (uintptr_t)w | (uintptr_t)y) & 15) == 0) {
+        const int vthreads = ((Hg / 8 + 31) / 32) * 32;
+        CELLM_RUN(gated_norm_add_vec8_kernel, dim3((unsigned)T, (unsigned)groups), vthreads, 0, stream, x, (const __nv_bfloat16*)m,
+                  (const __nv_bfloat16*)gate, (const __nv_bfloat16*)gate_bias, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, Hg, eps);
+        return CELLM_OK;
+    }
     const size_t smem = (size_t)H * sizeof(float);
     if (smem > 200 * 1024) return CELLM_ERR_SIZE;
     const int per = H / groups;

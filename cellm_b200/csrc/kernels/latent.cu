@@ -57,12 +57,17 @@ latent_prep_kernel(TA* __restrict__ q_plain, TA* __restrict__ q_full, const TP* 
     pdl_wait();
     const TP* row = proj + (size_t)t * ld;
     const int qw = dim + rot_dim, kw = rank + rot_dim;
+    // blockIdx.y = 0: the latent and the shared key part; 1..: a run of query heads each, so that a token's work is
+    // spread over several blocks when the tokens are few
+    if (blockIdx.y > 0) {
+    const int per = (heads + gridDim.y - 2) / (gridDim.y - 1);
+    const int h_lo = min(heads, ((int)blockIdx.y - 1) * per), h_hi = min(heads, h_lo + per);
     // queries: the unrotated part head by head; the rotated part turned, behind the kv_rank places of its head
-    for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) {
+    for (int i = h_lo * dim + threadIdx.x; i < h_hi * dim; i += blockDim.x) {
         const int h = i / dim, d = i - h * dim;
         q_plain[(size_t)t * heads * dim + i] = from_float<TA>(to_float(row[h * qw + d]));
     }
-    for (int i = threadIdx.x; i < heads * rot_dim; i += blockDim.x) {
+    for (int i = h_lo * rot_dim + threadIdx.x; i < h_hi * rot_dim; i += blockDim.x) {
         const int h = i / rot_dim, d = i - h * rot_dim;
         const TP* src = row + h * qw + dim;
         float v = to_float(src[d]);
@@ -72,6 +77,8 @@ latent_prep_kernel(TA* __restrict__ q_plain, TA* __restrict__ q_full, const TP* 
             v = (d & 1) ? v * cs[p] + other * sn[p] : v * cs[p] - other * sn[p];
         }
         q_full[((size_t)t * heads + h) * kw + rank + d] = from_float<TA>(v);
+    }
+    return;
     }
     // the latent: divided by its root mean square, times its weight; the shared key part turned; both to the cache
     const TP* down = row + (size_t)heads * qw;
@@ -111,8 +118,11 @@ CELLM_API int cellm_latent_prep(void* q_plain, void* q_full, const void* proj, l
     if (rot > 0 && !inv_freq) return CELLM_ERR_ARG;
     if (pool && (!block_table || page_size <= 0)) return CELLM_ERR_ARG;
     const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
+    // few tokens: a token's query heads in up to 8 blocks beside the block of its latent
+    const int qblocks = T >= 256 ? 1 : (heads < 8 ? heads : 8);
+    const dim3 grid((unsigned)T, (unsigned)(1 + qblocks));
 #define LAUNCH(TP, TA, TW)                                                                                              \
-    CELLM_RUN((latent_prep_kernel<TP, TA, TW>), T, 128, smem, stream, (TA*)q_plain, (TA*)q_full, (const TP*)proj, ld,    \
+    CELLM_RUN((latent_prep_kernel<TP, TA, TW>), grid, 128, smem, stream, (TA*)q_plain, (TA*)q_full, (const TP*)proj, ld,    \
               (const TW*)c_norm_w, eps, positions, seq_of_token, block_table, bt_stride, (TA*)pool, num_pages, page_size, \
               heads, dim, rot_dim, rank, rot, inv_freq, err)
     if (act_dtype == CELLM_F32 && proj_dtype == CELLM_F32 && w_dtype == CELLM_F32) LAUNCH(float, float, float);
@@ -166,11 +176,58 @@ head_product_kernel(TA* __restrict__ out, long long ldo, long long out_hs, const
     }
 }
 
+// A few tokens (decoding): the matrices are what has to be read, once. A block takes 16 output rows of one head, its
+// tokens' inputs wait in shared memory as floats, and each warp forms one output row at a time for all tokens: the
+// lanes stride over K, the sums meet by shuffles. K is summed in the same order for every token count up to HP_SMALL_T.
+#define HP_SMALL_T 16
+template <typename TA>
+__global__ void __launch_bounds__(128)
+head_product_small_kernel(TA* __restrict__ out, long long ldo, long long out_hs, const TA* __restrict__ in, long long ldi,
+                          long long in_hs, const TA* __restrict__ w, int T, int N, int K) {
+    extern __shared__ float xin[];       // [T][K]
+    pdl_trigger();
+    pdl_wait();
+    const int h = blockIdx.y, n0 = blockIdx.x * 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < T * K; i += blockDim.x) {
+        const int t = i / K, k = i - t * K;
+        xin[i] = to_float(in[(size_t)t * ldi + h * in_hs + k]);
+    }
+    __syncthreads();
+    const TA* wh = w + (size_t)h * N * K;
+    for (int n = n0 + warp; n < min(N, n0 + 16); n += 4) {
+        float acc[HP_SMALL_T];
+#pragma unroll
+        for (int t = 0; t < HP_SMALL_T; ++t) acc[t] = 0.f;
+        for (int k = lane; k < K; k += 32) {
+            const float wv = to_float(wh[(size_t)n * K + k]);
+#pragma unroll
+            for (int t = 0; t < HP_SMALL_T; ++t)
+                if (t < T) acc[t] = fmaf(xin[t * K + k], wv, acc[t]);
+        }
+#pragma unroll
+        for (int t = 0; t < HP_SMALL_T; ++t) {
+            if (t < T) {
+                const float v = warp_sum(acc[t]);
+                if (lane == 0) out[(size_t)t * ldo + h * out_hs + n] = from_float<TA>(v);
+            }
+        }
+    }
+}
+
 // in: [T, ldi] with head h at columns h * in_hs; w: [heads, N, K]; out: [T, ldo] with head h at columns h * out_hs.
 CELLM_API int cellm_head_product(void* out, long long ldo, long long out_hs, const void* in, long long ldi, long long in_hs,
                                  const void* w, int T, int heads, int N, int K, int dtype, cudaStream_t stream) {
     if (T <= 0 || heads <= 0 || N <= 0) return CELLM_OK;
     if (K <= 0) return CELLM_ERR_SIZE;
+    // (32-bit activations always take the tiles below: one order of the sums whatever the number of tokens)
+    if (dtype == CELLM_BF16 && T <= HP_SMALL_T && (size_t)T * K * sizeof(float) <= 48 * 1024) {
+        const dim3 sgrid((unsigned)((N + 15) / 16), (unsigned)heads);
+        const size_t smem = (size_t)T * K * sizeof(float);
+        CELLM_RUN(head_product_small_kernel<__nv_bfloat16>, sgrid, 128, smem, stream, (__nv_bfloat16*)out, ldo, out_hs,
+                  (const __nv_bfloat16*)in, ldi, in_hs, (const __nv_bfloat16*)w, T, N, K);
+        return CELLM_OK;
+    }
     const dim3 grid((unsigned)((N + HP_TILE - 1) / HP_TILE), (unsigned)((T + HP_TILE - 1) / HP_TILE), (unsigned)heads);
     const dim3 block(HP_TILE, 8);
     if (dtype == CELLM_F32)

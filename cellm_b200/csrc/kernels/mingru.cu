@@ -44,14 +44,88 @@ mingru_scan_kernel(TA* __restrict__ out, const TP* __restrict__ proj, long long 
     state[(size_t)slot * slot_stride + c] = S;
 }
 
+// Long portions: the recurrence is linear in S (S_t = a_t S_(t-1) + b_t with a = 1 - z, b = z c), so a portion is cut
+// into MG_SEGS runs of tokens that are walked side by side. A block is 32 channels times MG_SEGS runs. Each thread
+// first walks its run from zero and keeps (product of a, end value); the run's true start follows from the runs before
+// it (at most MG_SEGS - 1 steps of S <- A S + B, from the state the request brought); then the run is walked again from
+// that start and the outputs are written. The sums differ from the token-by-token walk only in rounding.
+#define MG_SEGS 32
+template <typename TP, typename TA, typename TW>
+__global__ void __launch_bounds__(32 * MG_SEGS)
+mingru_chunked_kernel(TA* __restrict__ out, const TP* __restrict__ proj, long long ld, const TW* __restrict__ bz,
+                      const TW* __restrict__ bx, float* __restrict__ state, long long slot_stride,
+                      const int* __restrict__ slot_ids, const int* __restrict__ cu_seqlens, int W, int n_slots,
+                      int* __restrict__ err) {
+    __shared__ float prod_s[MG_SEGS][33], end_s[MG_SEGS][33];
+    pdl_trigger();
+    const int lane = threadIdx.x, seg = threadIdx.y;
+    const int c = blockIdx.x * 32 + lane;
+    const int b = blockIdx.y;
+    const int slot = slot_ids[b];
+    const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
+    const bool slot_ok = slot >= 0 && slot < n_slots;
+    if (!slot_ok && lane == 0 && seg == 0 && blockIdx.x == 0) atomicOr(err, CELLM_DEV_BAD_SLOT);
+    const bool on = c < W && slot_ok;
+    const int per = (t1 - t0 + MG_SEGS - 1) / MG_SEGS;
+    const int lo = min(t1, t0 + seg * per), hi = min(t1, lo + per);
+    const float zb = (on && bz) ? to_float(bz[c]) : 0.f, xb = (on && bx) ? to_float(bx[c]) : 0.f;
+    const float S0 = on ? state[(size_t)slot * slot_stride + c] : 0.f;
+    pdl_wait();
+    float A = 1.f, E = 0.f;
+    if (on) {
+#pragma unroll 4
+        for (int t = lo; t < hi; ++t) {
+            const TP* row = proj + (size_t)t * ld;
+            const float z = sigmoid_f(to_float(row[c]) + zb);
+            const float u = to_float(row[W + c]) + xb;
+            const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+            A *= 1.0f - z;
+            E = (1.0f - z) * E + z * cand;
+        }
+    }
+    prod_s[seg][lane] = A;
+    end_s[seg][lane] = E;
+    __syncthreads();
+    float S = S0;
+    for (int k = 0; k < seg; ++k) S = prod_s[k][lane] * S + end_s[k][lane];
+    if (on) {
+#pragma unroll 4
+        for (int t = lo; t < hi; ++t) {
+            const TP* row = proj + (size_t)t * ld;
+            const float z = sigmoid_f(to_float(row[c]) + zb);
+            const float u = to_float(row[W + c]) + xb;
+            const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+            const float g = to_float(row[2 * W + c]);
+            S = (1.0f - z) * S + z * cand;
+            out[(size_t)t * W + c] = from_float<TA>(S * (g * sigmoid_f(g)));
+        }
+        if (seg == MG_SEGS - 1) state[(size_t)slot * slot_stride + c] = S;
+    }
+}
+
 // out: [T, W] activations; proj: [T, ld] = [pz | px | pg] (32-bit, or the activations' type); bz, bx: [W] or null;
-// state: [slots, slot_stride] float, read and updated in place.
+// state: [slots, slot_stride] float, read and updated in place. max_q_len: the longest portion of the step (0: unknown).
 CELLM_API int cellm_mingru_scan(void* out, const void* proj, long long ld, int proj_dtype, const void* bz, const void* bx,
                                 int w_dtype, float* state, long long slot_stride, const int* slot_ids, const int* cu_seqlens,
-                                int T, int B, int W, int n_slots, int act_dtype, int* err, cudaStream_t stream) {
+                                int T, int B, int W, int n_slots, int max_q_len, int act_dtype, int* err, cudaStream_t stream) {
     if (T <= 0 || B <= 0) return CELLM_OK;
     if (W <= 0 || ld < 3LL * W) return CELLM_ERR_SIZE;
     if (!state || !proj || !out) return CELLM_ERR_ARG;
+    // long portions under 16-bit activations walk their tokens in runs side by side (max_q_len: the longest portion if the
+    // host knows it, else 0); 32-bit activations always take the token-by-token walk, whose sums do not depend on the cut
+    if (act_dtype == CELLM_BF16 && proj_dtype == CELLM_F32 && max_q_len >= 4 * MG_SEGS) {
+        const dim3 cgrid((unsigned)((W + 31) / 32), (unsigned)B), cblock(32, MG_SEGS);
+        if (w_dtype == CELLM_BF16)
+            CELLM_RUN((mingru_chunked_kernel<float, __nv_bfloat16, __nv_bfloat16>), cgrid, cblock, 0, stream, (__nv_bfloat16*)out,
+                      (const float*)proj, ld, (const __nv_bfloat16*)bz, (const __nv_bfloat16*)bx, state, slot_stride, slot_ids,
+                      cu_seqlens, W, n_slots, err);
+        else if (w_dtype == CELLM_F32)
+            CELLM_RUN((mingru_chunked_kernel<float, __nv_bfloat16, float>), cgrid, cblock, 0, stream, (__nv_bfloat16*)out,
+                      (const float*)proj, ld, (const float*)bz, (const float*)bx, state, slot_stride, slot_ids, cu_seqlens, W,
+                      n_slots, err);
+        else return CELLM_ERR_DTYPE;
+        return CELLM_OK;
+    }
     const dim3 grid((unsigned)((W + 127) / 128), (unsigned)B);
 #define LAUNCH(TP, TA, TW)                                                                                              \
     CELLM_RUN((mingru_scan_kernel<TP, TA, TW>), grid, 128, 0, stream, (TA*)out, (const TP*)proj, ld, (const TW*)bz, (const TW*)bx, \

@@ -42,7 +42,7 @@ typedef int (*GatedNormAddFn)(P x, CP m, CP gate, CP gate_bias, CP w, int w_tag,
                               P stream);
 typedef int (*StreamCastFn)(P y, CP x, i64 n, int act_tag, P stream);
 typedef int (*MinGruScanFn)(P out, CP proj, i64 ld, int proj_tag, CP bz, CP bx, int w_tag, P state, i64 slot_stride, CP slot_ids, CP cu,
-                            int T, int B, int W, int n_slots, int act_tag, P err, P stream);
+                            int T, int B, int W, int n_slots, int max_q_len, int act_tag, P err, P stream);
 typedef int (*LatentPrepFn)(P q_plain, P q_full, CP proj, i64 ld, int proj_tag, CP c_norm_w, int w_tag, float eps, CP positions, CP seq,
                             CP bt, int bt_stride, P pool, int pages, int page_size, int T, int heads, int dim, int rot_dim, int rank,
                             int rot, CP inv_freq, int act_tag, P err, P stream);
@@ -123,7 +123,8 @@ struct Run {
 
     // The tensor-core product with a given tile shape and split; c: [M, N] (or [M, N/2] with the SwiGLU epilogue).
     void gemm_tc(void* c, const void* a, const ExecLinear& l, i64 M, i64 N, i64 lda, i64 out_dtype, i64 bn, i64 split_k,
-                 i64 epilogue) {
+                 i64 epilogue, i64 ldc = -1) {
+        if (ldc < 0) ldc = epilogue ? N / 2 : N;
         const i64 split = effective_split(l.K, split_k);
         // swapped tiles whose K split is one thread-block cluster (2..8 CTAs) sum their pieces through shared
         // memory: no workspace, no counters
@@ -138,7 +139,7 @@ struct Run {
         // plain tiles leave the sum of their K-split pieces to a second kernel; swapped tiles outside a cluster let
         // the last CTA of a tile sum them
         void* counters = (split > 1 && !in_cluster && bn < 0) ? s.counters : nullptr;
-        LAUNCH(fn<GemmTcFn>(FN_GEMM_TCGEN05)(c, a, l.w, (int)M, (int)N, (int)l.K, lda, l.ldw, epilogue ? N / 2 : N, (int)out_dtype, (int)bn,
+        LAUNCH(fn<GemmTcFn>(FN_GEMM_TCGEN05)(c, a, l.w, (int)M, (int)N, (int)l.K, lda, l.ldw, ldc, (int)out_dtype, (int)bn,
                                          (int)split_k, (int)epilogue, (int)p.static_flag, ws, counters, s.err, s.stream),
            "gemm_tcgen05");
         if (bn > 0 && split > 1) ++launches;          // the kernel that sums the K-split pieces
@@ -154,6 +155,27 @@ struct Run {
             i64 bn, split;
             plan_tiles(M, N, l.K, p.sms, &bn, &split);
             gemm_tc(c, a, l, M, N, lda, out_dtype, bn, split, 0);
+        }
+    }
+    // out[t, h * out_hs + n] = sum_k in[t, h * in_hs + k] * w[h][n][k] for per-head matrices w [heads, N, K]: many tokens
+    // under bfloat16 run the tensor-core product once a head (operands where TMA can fetch them: 16-byte rows), the
+    // rest one kernel over all heads
+    void head_products(void* out, i64 ldo, i64 out_hs, const void* in, i64 ldi, i64 in_hs, const void* w, i64 T, i64 heads, i64 N,
+                       i64 K) {
+        const bool tc = act == EXEC_BF16 && T >= 128 && K % 8 == 0 && ldi % 8 == 0 && in_hs % 8 == 0 && (N * K) % 8 == 0 &&
+                        ((uintptr_t)in % 16) == 0 && ((uintptr_t)w % 16) == 0;
+        if (!tc) {
+            LAUNCH(fn<HeadProductFn>(FN_HEAD_PRODUCT)(out, ldo, out_hs, in, ldi, in_hs, w, (int)T, (int)heads, (int)N, (int)K, (int)act,
+                                                  s.stream),
+                   "head_product");
+            return;
+        }
+        i64 bn, split;
+        plan_tiles(T, N, K, p.sms, &bn, &split);
+        for (i64 h = 0; h < heads; ++h) {
+            ExecLinear l{static_cast<const char*>(w) + h * N * K * 2, N, K, K, EXEC_BF16, 1};
+            gemm_tc(static_cast<char*>(out) + h * out_hs * 2, static_cast<const char*>(in) + h * in_hs * 2, l, T, N, ldi, act, bn, split,
+                    0, ldo);
         }
     }
     void* linear(const void* a, const ExecLinear& l, i64 M, i64 lda, i64 out_dtype, i64 N = -1) {
@@ -573,7 +595,7 @@ void Run::mingru(const MinGruParams& L, const ExecItem& it, const void* x, void*
     void* proj = linear(x, L.in_proj, T, H, EXEC_F32);
     void* y = arena.take(T * W * elt(act));
     LAUNCH(fn<MinGruScanFn>(FN_MINGRU_SCAN)(y, proj, 3 * W, (int)EXEC_F32, L.bz, L.bx, (int)L.b_dtype, it.state, it.slot_stride, s.slot_ids,
-                                        s.cu_seqlens, (int)T, (int)s.B, (int)W, (int)it.n_slots, (int)act, s.err, s.stream),
+                                        s.cu_seqlens, (int)T, (int)s.B, (int)W, (int)it.n_slots, (int)s.max_q_len, (int)act, s.err, s.stream),
            "mingru_scan");
     product(out, y, L.out_proj, T, W, act);
 }
@@ -589,9 +611,7 @@ void Run::latent_attention(const LatentAttentionParams& L, const ExecItem& it, c
                                         (int)L.rot, L.inv_freq, (int)act, s.err, s.stream),
            "latent_prep");
     // a head's query against the cached rows: [K_h^T q_h | rotated part]
-    LAUNCH(fn<HeadProductFn>(FN_HEAD_PRODUCT)(q_full, nh * kw, kw, q_plain, nh * L.dim, L.dim, L.absorb_k, (int)T, (int)nh, (int)L.rank,
-                                          (int)L.dim, (int)act, s.stream),
-           "head_product");
+    head_products(q_full, nh * kw, kw, q_plain, nh * L.dim, L.dim, L.absorb_k, T, nh, L.rank, L.dim);
     // every head reads the same rows (one key/value head); a value is a row's first `rank` entries
     void* o_lat = arena.take(T * nh * L.rank * e);
     // bfloat16 and sizes the tensor-core kernel takes (multiples of 16, value columns that split over its warps, tiles
@@ -627,9 +647,7 @@ void Run::latent_attention(const LatentAttentionParams& L, const ExecItem& it, c
                                                 (float)L.scale, 0, (int)act, s.err, s.stream),
            "attention_plain");
     void* o = arena.take(T * nh * L.vdim * e);
-    LAUNCH(fn<HeadProductFn>(FN_HEAD_PRODUCT)(o, nh * L.vdim, L.vdim, o_lat, nh * L.rank, L.rank, L.expand_v, (int)T, (int)nh, (int)L.vdim,
-                                          (int)L.rank, (int)act, s.stream),
-           "head_product");
+    head_products(o, nh * L.vdim, L.vdim, o_lat, nh * L.rank, L.rank, L.expand_v, T, nh, L.vdim, L.rank);
     product(out, o, L.out_proj, T, nh * L.vdim, act);
 }
 

@@ -223,9 +223,11 @@ def gated_norm_add(x: torch.Tensor, m: torch.Tensor, gate: Optional[torch.Tensor
 
 
 def mingru_scan(proj: torch.Tensor, bz: Optional[torch.Tensor], bx: Optional[torch.Tensor], state: torch.Tensor,
-                slot_ids: torch.Tensor, cu_seqlens: torch.Tensor, act_dtype: torch.dtype, err: torch.Tensor) -> torch.Tensor:
+                slot_ids: torch.Tensor, cu_seqlens: torch.Tensor, act_dtype: torch.dtype, err: torch.Tensor,
+                max_q_len: int = 0) -> torch.Tensor:
     """proj [T, 3W] = [z | candidate | output gate] pre-activations; state [slots, W] float32, read and updated in place.
-    Returns S_t * silu(gate) [T, W] in act_dtype."""
+    Returns S_t * silu(gate) [T, W] in act_dtype. `max_q_len`: the longest portion if the host knows it (long portions
+    under bfloat16 are walked in runs side by side)."""
     require_cuda(proj, bz, bx, state, slot_ids, cu_seqlens, err)
     T, W3 = proj.shape
     W = W3 // 3
@@ -234,7 +236,7 @@ def mingru_scan(proj: torch.Tensor, bz: Optional[torch.Tensor], bx: Optional[tor
     wt = tag(bz) if bz is not None else tag(act_dtype)
     out = torch.empty((T, W), dtype=act_dtype, device=proj.device)
     check(fn(_LIB, "cellm_mingru_scan")(ptr(out), ptr(proj), proj.stride(0), tag(proj), ptr(bz), ptr(bx), wt, ptr(state), state.stride(0),
-                                        ptr(slot_ids), ptr(cu_seqlens), T, cu_seqlens.numel() - 1, W, state.shape[0], tag(act_dtype),
+                                        ptr(slot_ids), ptr(cu_seqlens), T, cu_seqlens.numel() - 1, W, state.shape[0], int(max_q_len), tag(act_dtype),
                                         ptr(err), stream_of(proj)), "mingru_scan")
     return out
 

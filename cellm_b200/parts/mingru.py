@@ -67,7 +67,7 @@ class MinGRUMixer(Mixer):
         if rec is not None:
             return part_program(self.dtype, x.device, self.H).run_part(rec, x, ctx, cache)
         proj = self.in_proj(x, out_dtype=torch.float32)
-        y = ops.mingru_scan(proj, self.bz, self.bx, cache.state, ctx.slot_ids, ctx.cu_seqlens, self.dtype, ctx.err)
+        y = ops.mingru_scan(proj, self.bz, self.bx, cache.state, ctx.slot_ids, ctx.cu_seqlens, self.dtype, ctx.err, ctx.max_q_len)
         return self.out_proj(y)
 
 

@@ -314,6 +314,14 @@ def test_mingru_scan_whole_against_token_by_token(dtype):
     ops.mingru_scan(pd[:60], bzd, bxd, state3, i32([0]), i32([0, 60]), dtype, err)
     both = ops.mingru_scan(torch.cat([pd[:60], pd[60:]]), bzd, bxd, state3, i32([2, 0]), i32([0, 60, T]), dtype, err)
     assert torch.equal(both, out) and torch.equal(state3[0], state[2])
+    # long portions under bfloat16 are walked in runs side by side: the same recurrence up to rounding, also for
+    # a request of one token and one whose runs are not all full beside the long one
+    state4 = torch.zeros(3, W, device=DEV)
+    ops.mingru_scan(pd[:1], bzd, bxd, state4, i32([1]), i32([0, 1]), dtype, err)
+    runs = ops.mingru_scan(torch.cat([pd, pd[1:2]]), bzd, bxd, state4, i32([0, 1]), i32([0, T, T + 1]), dtype, err, max_q_len=T)
+    torch.testing.assert_close(runs[:T].cpu().double(), want, **tol)
+    torch.testing.assert_close(runs[T:].cpu().double(), want[1:2], **tol)
+    torch.testing.assert_close(state4[0].cpu().double(), S, rtol=1e-5, atol=1e-6)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
