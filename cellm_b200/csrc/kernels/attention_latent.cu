@@ -239,6 +239,7 @@ __global__ void latent_merge_kernel(__nv_bfloat16* __restrict__ out, const float
 
 // value columns per warp for a value width, or 0 if no form of the kernel takes it
 int value_columns(int dv) {
+    if (dv % 256 == 0 && dv / 256 <= 2) return 256;     // 8 warps with 128 accumulator registers each: the scores are formed twice, not four times
     if (dv % 128 == 0 && dv / 128 <= 4) return 128;
     if (dv % 64 == 0 && dv / 64 <= 4) return 64;
     if (dv % 32 == 0 && dv / 32 <= 8) return 32;
@@ -282,7 +283,8 @@ CELLM_API int cellm_attention_latent(void* out, float* part_o, float* part_ml, c
                   (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, cu_seqlens, ctx_lens, block_table, bt_stride, B, T,  \
                   num_pages, page_size, nh, kw, dv, scale_log2e, nsplit, err);                                             \
     } while (0)
-    if (dvw == 128) LAUNCH(128, 32, 512);
+    if (dvw == 256) LAUNCH(256, 32, 256);
+    else if (dvw == 128) LAUNCH(128, 32, 512);
     else if (dvw == 64) LAUNCH(64, 64, 512);
     else if (dvw == 32) LAUNCH(32, 32, 1024);
     else LAUNCH(16, 32, 1024);

@@ -130,6 +130,7 @@ CELLM_API int cellm_latent_prep(void* q_plain, void* q_full, const void* proj, l
     else if (act_dtype == CELLM_BF16 && proj_dtype == CELLM_F32 && w_dtype == CELLM_BF16) LAUNCH(float, __nv_bfloat16, __nv_bfloat16);
     else if (act_dtype == CELLM_BF16 && proj_dtype == CELLM_F32 && w_dtype == CELLM_F32) LAUNCH(float, __nv_bfloat16, float);
     else if (act_dtype == CELLM_BF16 && proj_dtype == CELLM_BF16 && w_dtype == CELLM_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+    else if (act_dtype == CELLM_BF16 && proj_dtype == CELLM_BF16 && w_dtype == CELLM_F32) LAUNCH(__nv_bfloat16, __nv_bfloat16, float);
     else return CELLM_ERR_DTYPE;
 #undef LAUNCH
     return CELLM_OK;
@@ -176,41 +177,52 @@ head_product_kernel(TA* __restrict__ out, long long ldo, long long out_hs, const
     }
 }
 
-// A few tokens (decoding): the matrices are what has to be read, once. A block takes 16 output rows of one head, its
-// tokens' inputs wait in shared memory as floats, and each warp forms one output row at a time for all tokens: the
-// lanes stride over K, the sums meet by shuffles. K is summed in the same order for every token count up to HP_SMALL_T.
+// A few tokens (decoding, bfloat16): the matrices are what has to be read, once. A block takes 32 output rows of one
+// head; the tokens' inputs wait in shared memory as floats; four neighbouring threads share a row, each over a quarter
+// of K in 16-byte loads, and add their sums by two shuffles. K (a multiple of 32) is summed in the same order for every
+// token count up to HP_SMALL_T.
 #define HP_SMALL_T 16
-template <typename TA>
 __global__ void __launch_bounds__(128)
-head_product_small_kernel(TA* __restrict__ out, long long ldo, long long out_hs, const TA* __restrict__ in, long long ldi,
-                          long long in_hs, const TA* __restrict__ w, int T, int N, int K) {
+head_product_small_kernel(__nv_bfloat16* __restrict__ out, long long ldo, long long out_hs, const __nv_bfloat16* __restrict__ in,
+                          long long ldi, long long in_hs, const __nv_bfloat16* __restrict__ w, int T, int N, int K) {
     extern __shared__ float xin[];       // [T][K]
     pdl_trigger();
+    const int h = blockIdx.y;
+    const int n = blockIdx.x * 32 + (threadIdx.x >> 2), kq = threadIdx.x & 3;
+    const int kn = K / 4;
+    const bool on = n < N;
+    const __nv_bfloat16* wr = w + ((size_t)h * N + (on ? n : 0)) * K + kq * kn;
     pdl_wait();
-    const int h = blockIdx.y, n0 = blockIdx.x * 16;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int i = threadIdx.x; i < T * K; i += blockDim.x) {
         const int t = i / K, k = i - t * K;
-        xin[i] = to_float(in[(size_t)t * ldi + h * in_hs + k]);
+        xin[i] = __bfloat162float(in[(size_t)t * ldi + h * in_hs + k]);
     }
     __syncthreads();
-    const TA* wh = w + (size_t)h * N * K;
-    for (int n = n0 + warp; n < min(N, n0 + 16); n += 4) {
-        float acc[HP_SMALL_T];
+    float acc[HP_SMALL_T];
 #pragma unroll
-        for (int t = 0; t < HP_SMALL_T; ++t) acc[t] = 0.f;
-        for (int k = lane; k < K; k += 32) {
-            const float wv = to_float(wh[(size_t)n * K + k]);
+    for (int t = 0; t < HP_SMALL_T; ++t) acc[t] = 0.f;
+    for (int k0 = 0; k0 < kn; k0 += 8) {
+        const uint4 wq = *reinterpret_cast<const uint4*>(wr + k0);
+        const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wq);
+        float wv[8];
 #pragma unroll
-            for (int t = 0; t < HP_SMALL_T; ++t)
-                if (t < T) acc[t] = fmaf(xin[t * K + k], wv, acc[t]);
-        }
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(wp[j]); wv[2 * j] = f.x; wv[2 * j + 1] = f.y; }
+        const float* xr = xin + kq * kn + k0;
 #pragma unroll
         for (int t = 0; t < HP_SMALL_T; ++t) {
             if (t < T) {
-                const float v = warp_sum(acc[t]);
-                if (lane == 0) out[(size_t)t * ldo + h * out_hs + n] = from_float<TA>(v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[t] = fmaf(xr[t * K + j], wv[j], acc[t]);
             }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < HP_SMALL_T; ++t) {
+        if (t < T) {
+            float v = acc[t];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            if (kq == 0 && on) out[(size_t)t * ldo + h * out_hs + n] = __float2bfloat16_rn(v);
         }
     }
 }
@@ -221,10 +233,11 @@ CELLM_API int cellm_head_product(void* out, long long ldo, long long out_hs, con
     if (T <= 0 || heads <= 0 || N <= 0) return CELLM_OK;
     if (K <= 0) return CELLM_ERR_SIZE;
     // (32-bit activations always take the tiles below: one order of the sums whatever the number of tokens)
-    if (dtype == CELLM_BF16 && T <= HP_SMALL_T && (size_t)T * K * sizeof(float) <= 48 * 1024) {
-        const dim3 sgrid((unsigned)((N + 15) / 16), (unsigned)heads);
+    if (dtype == CELLM_BF16 && T <= HP_SMALL_T && (size_t)T * K * sizeof(float) <= 48 * 1024 && (K & 31) == 0 &&
+        ((uintptr_t)w & 15) == 0) {
+        const dim3 sgrid((unsigned)((N + 31) / 32), (unsigned)heads);
         const size_t smem = (size_t)T * K * sizeof(float);
-        CELLM_RUN(head_product_small_kernel<__nv_bfloat16>, sgrid, 128, smem, stream, (__nv_bfloat16*)out, ldo, out_hs,
+        CELLM_RUN(head_product_small_kernel, sgrid, 128, smem, stream, (__nv_bfloat16*)out, ldo, out_hs,
                   (const __nv_bfloat16*)in, ldi, in_hs, (const __nv_bfloat16*)w, T, N, K);
         return CELLM_OK;
     }

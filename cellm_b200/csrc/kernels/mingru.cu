@@ -45,21 +45,22 @@ mingru_scan_kernel(TA* __restrict__ out, const TP* __restrict__ proj, long long 
 }
 
 // Long portions: the recurrence is linear in S (S_t = a_t S_(t-1) + b_t with a = 1 - z, b = z c), so a portion is cut
-// into MG_SEGS runs of tokens that are walked side by side. A block is 32 channels times MG_SEGS runs. Each thread
+// into MG_SEGS runs of tokens that are walked side by side. A block is MG_CH channels times MG_SEGS runs (a half warp reads 16 neighbouring channels of a token). Each thread
 // first walks its run from zero and keeps (product of a, end value); the run's true start follows from the runs before
 // it (at most MG_SEGS - 1 steps of S <- A S + B, from the state the request brought); then the run is walked again from
 // that start and the outputs are written. The sums differ from the token-by-token walk only in rounding.
-#define MG_SEGS 32
+#define MG_SEGS 64
+#define MG_CH 16
 template <typename TP, typename TA, typename TW>
-__global__ void __launch_bounds__(32 * MG_SEGS)
+__global__ void __launch_bounds__(MG_CH * MG_SEGS)
 mingru_chunked_kernel(TA* __restrict__ out, const TP* __restrict__ proj, long long ld, const TW* __restrict__ bz,
                       const TW* __restrict__ bx, float* __restrict__ state, long long slot_stride,
                       const int* __restrict__ slot_ids, const int* __restrict__ cu_seqlens, int W, int n_slots,
                       int* __restrict__ err) {
-    __shared__ float prod_s[MG_SEGS][33], end_s[MG_SEGS][33];
+    __shared__ float prod_s[MG_SEGS][MG_CH + 1], end_s[MG_SEGS][MG_CH + 1];
     pdl_trigger();
     const int lane = threadIdx.x, seg = threadIdx.y;
-    const int c = blockIdx.x * 32 + lane;
+    const int c = blockIdx.x * MG_CH + lane;
     const int b = blockIdx.y;
     const int slot = slot_ids[b];
     const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
@@ -113,17 +114,17 @@ CELLM_API int cellm_mingru_scan(void* out, const void* proj, long long ld, int p
     if (!state || !proj || !out) return CELLM_ERR_ARG;
     // long portions under 16-bit activations walk their tokens in runs side by side (max_q_len: the longest portion if the
     // host knows it, else 0); 32-bit activations always take the token-by-token walk, whose sums do not depend on the cut
-    if (act_dtype == CELLM_BF16 && proj_dtype == CELLM_F32 && max_q_len >= 4 * MG_SEGS) {
-        const dim3 cgrid((unsigned)((W + 31) / 32), (unsigned)B), cblock(32, MG_SEGS);
-        if (w_dtype == CELLM_BF16)
-            CELLM_RUN((mingru_chunked_kernel<float, __nv_bfloat16, __nv_bfloat16>), cgrid, cblock, 0, stream, (__nv_bfloat16*)out,
-                      (const float*)proj, ld, (const __nv_bfloat16*)bz, (const __nv_bfloat16*)bx, state, slot_stride, slot_ids,
-                      cu_seqlens, W, n_slots, err);
-        else if (w_dtype == CELLM_F32)
-            CELLM_RUN((mingru_chunked_kernel<float, __nv_bfloat16, float>), cgrid, cblock, 0, stream, (__nv_bfloat16*)out,
-                      (const float*)proj, ld, (const float*)bz, (const float*)bx, state, slot_stride, slot_ids, cu_seqlens, W,
-                      n_slots, err);
+    if (act_dtype == CELLM_BF16 && max_q_len >= 2 * MG_SEGS) {
+        const dim3 cgrid((unsigned)((W + MG_CH - 1) / MG_CH), (unsigned)B), cblock(MG_CH, MG_SEGS);
+#define CHUNKED(TP, TW)                                                                                                 \
+        CELLM_RUN((mingru_chunked_kernel<TP, __nv_bfloat16, TW>), cgrid, cblock, 0, stream, (__nv_bfloat16*)out, (const TP*)proj, ld, \
+                  (const TW*)bz, (const TW*)bx, state, slot_stride, slot_ids, cu_seqlens, W, n_slots, err)
+        if (proj_dtype == CELLM_BF16 && w_dtype == CELLM_BF16) CHUNKED(__nv_bfloat16, __nv_bfloat16);
+        else if (proj_dtype == CELLM_BF16 && w_dtype == CELLM_F32) CHUNKED(__nv_bfloat16, float);
+        else if (w_dtype == CELLM_BF16) CHUNKED(float, __nv_bfloat16);
+        else if (w_dtype == CELLM_F32) CHUNKED(float, float);
         else return CELLM_ERR_DTYPE;
+#undef CHUNKED
         return CELLM_OK;
     }
     const dim3 grid((unsigned)((W + 127) / 128), (unsigned)B);
@@ -135,6 +136,7 @@ CELLM_API int cellm_mingru_scan(void* out, const void* proj, long long ld, int p
     else if (act_dtype == CELLM_BF16 && proj_dtype == CELLM_F32 && w_dtype == CELLM_BF16) LAUNCH(float, __nv_bfloat16, __nv_bfloat16);
     else if (act_dtype == CELLM_BF16 && proj_dtype == CELLM_F32 && w_dtype == CELLM_F32) LAUNCH(float, __nv_bfloat16, float);
     else if (act_dtype == CELLM_BF16 && proj_dtype == CELLM_BF16 && w_dtype == CELLM_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+    else if (act_dtype == CELLM_BF16 && proj_dtype == CELLM_BF16 && w_dtype == CELLM_F32) LAUNCH(__nv_bfloat16, __nv_bfloat16, float);
     else return CELLM_ERR_DTYPE;
 #undef LAUNCH
     return CELLM_OK;

@@ -591,10 +591,11 @@ void Run::gated_mlp(const GatedMlpParams& L, const void* x, void* out) {
 void Run::mingru(const MinGruParams& L, const ExecItem& it, const void* x, void* out) {
     const i64 T = s.T, H = p.H, W = L.width;
     if (!it.state) throw std::runtime_error("executor: a recurrent mixer without a state slot");
-    // the three projections side by side in 32-bit: everything that enters the recurrence is formed from the sums
-    void* proj = linear(x, L.in_proj, T, H, EXEC_F32);
+    // the three projections side by side, in the activations' type like every product's output; gates, candidate and
+    // state are formed from them in 32-bit
+    void* proj = linear(x, L.in_proj, T, H, act);
     void* y = arena.take(T * W * elt(act));
-    LAUNCH(fn<MinGruScanFn>(FN_MINGRU_SCAN)(y, proj, 3 * W, (int)EXEC_F32, L.bz, L.bx, (int)L.b_dtype, it.state, it.slot_stride, s.slot_ids,
+    LAUNCH(fn<MinGruScanFn>(FN_MINGRU_SCAN)(y, proj, 3 * W, (int)act, L.bz, L.bx, (int)L.b_dtype, it.state, it.slot_stride, s.slot_ids,
                                         s.cu_seqlens, (int)T, (int)s.B, (int)W, (int)it.n_slots, (int)s.max_q_len, (int)act, s.err, s.stream),
            "mingru_scan");
     product(out, y, L.out_proj, T, W, act);
@@ -602,10 +603,10 @@ void Run::mingru(const MinGruParams& L, const ExecItem& it, const void* x, void*
 
 void Run::latent_attention(const LatentAttentionParams& L, const ExecItem& it, const void* x, void* out) {
     const i64 T = s.T, H = p.H, nh = L.heads, kw = L.rank + L.rot_dim, e = elt(act);
-    void* proj = linear(x, L.in_proj, T, H, EXEC_F32);
+    void* proj = linear(x, L.in_proj, T, H, act);
     void* q_plain = arena.take(T * nh * L.dim * e);
     void* q_full = arena.take(T * nh * kw * e);
-    LAUNCH(fn<LatentPrepFn>(FN_LATENT_PREP)(q_plain, q_full, proj, L.in_proj.N, (int)EXEC_F32, L.c_norm_w, (int)L.c_norm_dtype, (float)L.eps,
+    LAUNCH(fn<LatentPrepFn>(FN_LATENT_PREP)(q_plain, q_full, proj, L.in_proj.N, (int)act, L.c_norm_w, (int)L.c_norm_dtype, (float)L.eps,
                                         s.positions, s.seq_of_token, it.block_table, (int)it.bt_stride, it.writes ? it.k : nullptr,
                                         (int)it.num_pages, (int)it.page_size, (int)T, (int)nh, (int)L.dim, (int)L.rot_dim, (int)L.rank,
                                         (int)L.rot, L.inv_freq, (int)act, s.err, s.stream),
@@ -617,7 +618,8 @@ void Run::latent_attention(const LatentAttentionParams& L, const ExecItem& it, c
     // bfloat16 and sizes the tensor-core kernel takes (multiples of 16, value columns that split over its warps, tiles
     // that fit shared memory): 64 (token, head) rows a CTA; the keys in pieces when the tiles alone leave SMs idle
     i64 dvw = 0;
-    if (L.rank % 128 == 0 && L.rank / 128 <= 4) dvw = 128;
+    if (L.rank % 256 == 0 && L.rank / 256 <= 2) dvw = 256;
+    else if (L.rank % 128 == 0 && L.rank / 128 <= 4) dvw = 128;
     else if (L.rank % 64 == 0 && L.rank / 64 <= 4) dvw = 64;
     else if (L.rank % 32 == 0 && L.rank / 32 <= 8) dvw = 32;
     else if (L.rank % 16 == 0 && L.rank / 16 <= 8) dvw = 16;
