@@ -61,17 +61,26 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
         const __nv_bfloat16* src = q + ((size_t)t_base * nh + (ok ? r : 0)) * kw + chunk * 8;
         cp_async16(q_s + row * stride + chunk * 8, src, ok ? 16 : 0);
     }
+    // The rows of a block's keys are looked up first, all at once (one thread a key), so that the copies that follow do
+    // not each wait for a load of the block table.
+    __shared__ long long row_at[2][BN];
     auto load_k = [&](int kb, int stage) {
+        if (threadIdx.x < BN) {
+            const int j = kb * BN + threadIdx.x;
+            long long at = -1;
+            if (j < key_end) {
+                const int page = bt[j / page_size];
+                if (page < 0 || page >= num_pages) atomicOr(err, CELLM_DEV_BAD_PAGE);
+                else at = ((long long)page * page_size + j % page_size) * kw;
+            }
+            row_at[stage][threadIdx.x] = at;
+        }
+        __syncthreads();
         __nv_bfloat16* ks = k_s + stage * BN * stride;
         for (int i = threadIdx.x; i < BN * CH; i += threads) {
-            const int row = i / CH, chunk = i - row * CH, j = kb * BN + row;
-            int page = -1;
-            if (j < key_end) {
-                page = bt[j / page_size];
-                if (page < 0 || page >= num_pages) { atomicOr(err, CELLM_DEV_BAD_PAGE); page = -1; }
-            }
-            const size_t off = page >= 0 ? ((size_t)page * page_size + j % page_size) * kw + chunk * 8 : 0;
-            cp_async16(ks + row * stride + chunk * 8, pool + off, page >= 0 ? 16 : 0);
+            const int row = i / CH, chunk = i - row * CH;
+            const long long at = row_at[stage][row];
+            cp_async16(ks + row * stride + chunk * 8, pool + (at >= 0 ? at + chunk * 8 : 0), at >= 0 ? 16 : 0);
         }
     };
     if (my_begin < my_end) load_k(my_begin, 0);

@@ -177,9 +177,9 @@ head_product_kernel(TA* __restrict__ out, long long ldo, long long out_hs, const
     }
 }
 
-// A few tokens (decoding, bfloat16): the matrices are what has to be read, once. A block takes 32 output rows of one
-// head; the tokens' inputs wait in shared memory as floats; four neighbouring threads share a row, each over a quarter
-// of K in 16-byte loads, and add their sums by two shuffles. K (a multiple of 32) is summed in the same order for every
+// A few tokens (decoding, bfloat16): the matrices are what has to be read, once. A block takes 16 output rows of one
+// head; the tokens' inputs wait in shared memory as floats; eight neighbouring threads share a row, each over an eighth
+// of K in 16-byte loads, and add their sums by three shuffles. K (a multiple of 64) is summed in the same order for every
 // token count up to HP_SMALL_T.
 #define HP_SMALL_T 16
 __global__ void __launch_bounds__(128)
@@ -188,8 +188,8 @@ head_product_small_kernel(__nv_bfloat16* __restrict__ out, long long ldo, long l
     extern __shared__ float xin[];       // [T][K]
     pdl_trigger();
     const int h = blockIdx.y;
-    const int n = blockIdx.x * 32 + (threadIdx.x >> 2), kq = threadIdx.x & 3;
-    const int kn = K / 4;
+    const int n = blockIdx.x * 16 + (threadIdx.x >> 3), kq = threadIdx.x & 7;
+    const int kn = K / 8;
     const bool on = n < N;
     const __nv_bfloat16* wr = w + ((size_t)h * N + (on ? n : 0)) * K + kq * kn;
     pdl_wait();
@@ -201,6 +201,7 @@ head_product_small_kernel(__nv_bfloat16* __restrict__ out, long long ldo, long l
     float acc[HP_SMALL_T];
 #pragma unroll
     for (int t = 0; t < HP_SMALL_T; ++t) acc[t] = 0.f;
+#pragma unroll 2
     for (int k0 = 0; k0 < kn; k0 += 8) {
         const uint4 wq = *reinterpret_cast<const uint4*>(wr + k0);
         const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wq);
@@ -222,6 +223,7 @@ head_product_small_kernel(__nv_bfloat16* __restrict__ out, long long ldo, long l
             float v = acc[t];
             v += __shfl_xor_sync(0xffffffffu, v, 1);
             v += __shfl_xor_sync(0xffffffffu, v, 2);
+            v += __shfl_xor_sync(0xffffffffu, v, 4);
             if (kq == 0 && on) out[(size_t)t * ldo + h * out_hs + n] = __float2bfloat16_rn(v);
         }
     }
@@ -233,9 +235,9 @@ CELLM_API int cellm_head_product(void* out, long long ldo, long long out_hs, con
     if (T <= 0 || heads <= 0 || N <= 0) return CELLM_OK;
     if (K <= 0) return CELLM_ERR_SIZE;
     // (32-bit activations always take the tiles below: one order of the sums whatever the number of tokens)
-    if (dtype == CELLM_BF16 && T <= HP_SMALL_T && (size_t)T * K * sizeof(float) <= 48 * 1024 && (K & 31) == 0 &&
+    if (dtype == CELLM_BF16 && T <= HP_SMALL_T && (size_t)T * K * sizeof(float) <= 48 * 1024 && (K & 63) == 0 &&
         ((uintptr_t)w & 15) == 0) {
-        const dim3 sgrid((unsigned)((N + 31) / 32), (unsigned)heads);
+        const dim3 sgrid((unsigned)((N + 15) / 16), (unsigned)heads);
         const size_t smem = (size_t)T * K * sizeof(float);
         CELLM_RUN(head_product_small_kernel, sgrid, 128, smem, stream, (__nv_bfloat16*)out, ldo, out_hs,
                   (const __nv_bfloat16*)in, ldi, in_hs, (const __nv_bfloat16*)w, T, N, K);

@@ -338,6 +338,17 @@ def test_head_product_with_pitches(dtype):
     assert float(out[:, :, :3].abs().max()) == 0.0 and float(out[:, :, 3 + N:].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("T,heads,N,K", [(5, 3, 40, 128), (16, 2, 16, 64), (1, 4, 100, 192)])
+def test_head_product_of_few_tokens(T, heads, N, K):
+    """bfloat16 and at most 16 tokens: the form that reads each matrix row once."""
+    from cellm_b200 import ops
+    g = torch.Generator().manual_seed(6)
+    x, w = _t(torch.randn(T, heads, K, generator=g), torch.bfloat16), _t(torch.randn(heads, N, K, generator=g), torch.bfloat16)
+    out = ops.head_product(x, w)
+    want = torch.einsum("thk,hnk->thn", x.cpu().double(), w.cpu().double())
+    torch.testing.assert_close(out.cpu().double(), want, rtol=2e-2, atol=8e-2)
+
+
 @pytest.mark.parametrize("act", ["silu", "gelu_tanh"])
 def test_gated_act(act):
     from cellm_b200 import ops
