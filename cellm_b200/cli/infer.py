@@ -8,7 +8,7 @@ import time
 
 
 def main(argv=None) -> int:
-    ap = argparse.ArgumentParser(prog="infer", description="Inference for an LFM2 model folder on one B200")
+    ap = argparse.ArgumentParser(prog="infer", description="Inference for a model folder (any registered architecture) on one B200")
     from .common import add_model_options, default_blocks, parse_tokens, resolve_model
     add_model_options(ap)
     ap.add_argument("--tokenizer", help="path to a HuggingFace tokenizer.json (needed with --prompt)")

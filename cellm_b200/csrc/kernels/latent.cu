@@ -184,7 +184,7 @@ head_product_kernel(TA* __restrict__ out, long long ldo, long long out_hs, const
 #define HP_SMALL_T 16
 __global__ void __launch_bounds__(128)
 head_product_small_kernel(__nv_bfloat16* __restrict__ out, long long ldo, long long out_hs, const __nv_bfloat16* __restrict__ in,
-                          long long ldi, long long in_hs, const __nv_bfloat16* __restrict__ w, int T, int N, int K) {
+                          long long ldi, long long in_hs, const __nv_bfloat16* __restrict__ w, int T, int N, int K, int vec_in) {
     extern __shared__ float xin[];       // [T][K]
     pdl_trigger();
     const int h = blockIdx.y;
@@ -193,9 +193,25 @@ head_product_small_kernel(__nv_bfloat16* __restrict__ out, long long ldo, long l
     const bool on = n < N;
     const __nv_bfloat16* wr = w + ((size_t)h * N + (on ? n : 0)) * K + kq * kn;
     pdl_wait();
-    for (int i = threadIdx.x; i < T * K; i += blockDim.x) {
-        const int t = i / K, k = i - t * K;
-        xin[i] = __bfloat162float(in[(size_t)t * ldi + h * in_hs + k]);
+    if (vec_in) {                        // the inputs' rows start on 16-byte borders: eight values a load
+        const int K8 = K / 8;
+#pragma unroll 4
+        for (int i = threadIdx.x; i < T * K8; i += blockDim.x) {
+            const int t = i / K8, k = (i - t * K8) * 8;
+            const uint4 q = *reinterpret_cast<const uint4*>(in + (size_t)t * ldi + h * in_hs + k);
+            const __nv_bfloat162* qp = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(qp[j]);
+                xin[t * K + k + 2 * j] = f.x;
+                xin[t * K + k + 2 * j + 1] = f.y;
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < T * K; i += blockDim.x) {
+            const int t = i / K, k = i - t * K;
+            xin[i] = __bfloat162float(in[(size_t)t * ldi + h * in_hs + k]);
+        }
     }
     __syncthreads();
     float acc[HP_SMALL_T];
@@ -240,7 +256,8 @@ CELLM_API int cellm_head_product(void* out, long long ldo, long long out_hs, con
         const dim3 sgrid((unsigned)((N + 15) / 16), (unsigned)heads);
         const size_t smem = (size_t)T * K * sizeof(float);
         CELLM_RUN(head_product_small_kernel, sgrid, 128, smem, stream, (__nv_bfloat16*)out, ldo, out_hs,
-                  (const __nv_bfloat16*)in, ldi, in_hs, (const __nv_bfloat16*)w, T, N, K);
+                  (const __nv_bfloat16*)in, ldi, in_hs, (const __nv_bfloat16*)w, T, N, K,
+                  (int)((((uintptr_t)in & 15) == 0) && (ldi & 7) == 0 && (in_hs & 7) == 0));
         return CELLM_OK;
     }
     const dim3 grid((unsigned)((N + HP_TILE - 1) / HP_TILE), (unsigned)((T + HP_TILE - 1) / HP_TILE), (unsigned)heads);

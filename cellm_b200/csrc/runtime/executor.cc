@@ -628,7 +628,10 @@ void Run::latent_attention(const LatentAttentionParams& L, const ExecItem& it, c
         i64 n_tiles = 0;
         for (i64 b = 0; b < s.B; ++b) n_tiles += ceil_div(s.q_lens[b] * nh, 64);
         const i64 blocks = ceil_div(s.max_total_len, bn);
-        const i64 nsplit = std::max<i64>(1, std::min(ceil_div(2 * p.sms, n_tiles), blocks / 2));
+        // pieces of the keys: what fills the SMs once (two CTAs an SM where two tiles of this width fit its shared
+        // memory), of at least two blocks of keys each
+        const i64 per_sm = std::min<i64>(2, std::max<i64>(1, 227 * 1024 / ((64 + 2 * bn) * (kw + 8) * 2)));
+        const i64 nsplit = std::max<i64>(1, std::min(ceil_div(per_sm * p.sms, n_tiles), blocks / 2));
         void *part_o = nullptr, *part_ml = nullptr;
         if (nsplit > 1) {
             const i64 rows = T * nh;

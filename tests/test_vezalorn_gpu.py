@@ -432,3 +432,38 @@ def test_latent_attention_takes_the_tensor_core_kernel(models):
     before = program.CALLS["cellm_attention_latent"]
     run_trace(folder, "float32", traces.whole({"r0": reqs["r0"]}), 16)
     assert program.CALLS["cellm_attention_latent"] == before
+
+
+# --------------------------------------------------------------------------------------------- command lines
+def test_command_lines_take_the_design(models, tmp_path):
+    """bin/infer generates greedily from a folder of this design as the plain model does; bin/trace_run replays a mixed
+    trace of it from standard input."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    folder, reqs, ref = models["a"]
+    cfg, w = load_plain(folder)
+    prompt = reqs["r1"]
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "infer"), "--model", folder, "--dtype", "float32", "--tokens",
+                        ",".join(map(str, prompt)), "--gen", "6", "--temperature", "0", "--stop-eos", "false",
+                        "--tokens-per-block", "8"], capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-3000:]
+    out = [int(t) for t in [l for l in p.stdout.splitlines() if l.startswith("tokens:")][0].split(":")[1].split(",")]
+    seq = list(prompt) + out[:-1]
+    want = plain.forward(cfg, w, seq)[len(prompt) - 1:].numpy()
+    tol = 2 * K["float32"] * (1 + np.abs(want).max())
+    assert all(want[j].max() - want[j][t] <= tol for j, t in enumerate(out))
+    steps = traces.mixed(reqs, seed=4)
+    out_dir = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", "bfloat16",
+                        "--out", str(out_dir), "--max-tokens", str(traces.max_live_tokens(steps))],
+                       input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-3000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    outs = []
+    for s in steps:
+        n_want = sum(len(e["want"]) for e in s["entries"])
+        outs.append(np.fromfile(out_dir / f"{s['step']}.f32", dtype="<f4").reshape(n_want, cfg["vocab"]) if n_want else None)
+    got = traces.collect(steps, outs)
+    for rid, toks in reqs.items():
+        check_close(traces.as_matrix(got[rid], len(toks)), ref[rid], "bfloat16", f"trace_run {rid}")
