@@ -257,6 +257,64 @@ int value_columns(int dv) {
 }
 int keys_per_block(int dvw) { return dvw == 64 ? 64 : 32; }
 
+// Per-head products on the tensor cores: out[t, h, n] = sum_k in[t, h, k] * w[h][n][k]. A CTA forms 64 tokens by 64
+// outputs of one head: both operands' tiles wait whole in shared memory (K at most 512), each of the four warps forms
+// 16 tokens by 64 outputs as the attention forms its scores (rows of `in` against rows of `w`).
+__global__ void __launch_bounds__(128)
+head_product_mma_kernel(__nv_bfloat16* __restrict__ out, long long ldo, long long out_hs, const __nv_bfloat16* __restrict__ in,
+                        long long ldi, long long in_hs, const __nv_bfloat16* __restrict__ w, int T, int N, int K) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    const int stride = K + 8;
+    __nv_bfloat16* a_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* w_s = a_s + 64 * stride;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.z, t0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+    const int CH = K / 8;
+    pdl_trigger();
+    const __nv_bfloat16* wh = w + (size_t)h * N * K;
+    for (int i = threadIdx.x; i < 64 * CH; i += 128) {          // the matrices are not the work of the kernel before this one
+        const int row = i / CH, chunk = i - row * CH, n = n0 + row;
+        cp_async16(w_s + row * stride + chunk * 8, wh + (size_t)(n < N ? n : 0) * K + chunk * 8, n < N ? 16 : 0);
+    }
+    pdl_wait();
+    for (int i = threadIdx.x; i < 64 * CH; i += 128) {
+        const int row = i / CH, chunk = i - row * CH, t = t0 + row;
+        cp_async16(a_s + row * stride + chunk * 8, in + (size_t)(t < T ? t : 0) * ldi + h * in_hs + chunk * 8, t < T ? 16 : 0);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    float c[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
+    const __nv_bfloat16* a_row = a_s + (warp * 16 + (lane & 15)) * stride + (lane >> 4) * 8;
+    const __nv_bfloat16* w_row = w_s + ((lane & 7) + ((lane >> 4) << 3)) * stride + ((lane >> 3) & 1) * 8;
+#pragma unroll 2
+    for (int k0 = 0; k0 < K; k0 += 16) {
+        uint32_t af[4];
+        ldmatrix_x4(af, a_row + k0);
+#pragma unroll
+        for (int n2 = 0; n2 < 4; ++n2) {
+            uint32_t wf[4];
+            ldmatrix_x4(wf, w_row + n2 * 16 * stride + k0);
+            mma_bf16(c[2 * n2], af, wf[0], wf[1]);
+            mma_bf16(c[2 * n2 + 1], af, wf[2], wf[3]);
+        }
+    }
+    const int ta = t0 + warp * 16 + (lane >> 2), tb = ta + 8;
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+        const int col = n0 + n * 8 + (lane & 3) * 2;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            if (col + e < N) {
+                if (ta < T) out[(size_t)ta * ldo + h * out_hs + col + e] = __float2bfloat16_rn(c[n][e]);
+                if (tb < T) out[(size_t)tb * ldo + h * out_hs + col + e] = __float2bfloat16_rn(c[n][2 + e]);
+            }
+        }
+    }
+}
+
 }  // namespace
 
 // 1 if the kernel takes rows of kw values whose first dv are the value (else the plain kernel serves them)
@@ -301,5 +359,20 @@ CELLM_API int cellm_attention_latent(void* out, float* part_o, float* part_ml, c
     if (nsplit > 1)
         CELLM_RUN(latent_merge_kernel, (unsigned)((size_t)T * nh), dv >= 256 ? 256 : (dv >= 128 ? 128 : 64), (size_t)nsplit * sizeof(float), stream, (__nv_bfloat16*)out, part_o,
                   part_ml, (size_t)T * nh, dv, nsplit);
+    return CELLM_OK;
+}
+
+// Per-head products of many tokens: in [T, ldi] with head h at columns h * in_hs (K values, 16-byte aligned), w [heads, N,
+// K], out [T, ldo] with head h at columns h * out_hs. K a multiple of 16 and at most 512.
+CELLM_API int cellm_head_product_mma(void* out, long long ldo, long long out_hs, const void* in, long long ldi, long long in_hs,
+                                     const void* w, int T, int heads, int N, int K, cudaStream_t stream) {
+    if (T <= 0 || heads <= 0 || N <= 0) return CELLM_OK;
+    if (K <= 0 || (K & 15) || K > 512) return CELLM_ERR_SIZE;
+    if (((uintptr_t)in & 15) || ((uintptr_t)w & 15) || (ldi & 7) || (in_hs & 7)) return CELLM_ERR_ALIGN;
+    const size_t smem = (size_t)2 * 64 * (K + 8) * 2;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(head_product_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const dim3 grid((unsigned)((N + 63) / 64), (unsigned)((T + 63) / 64), (unsigned)heads);
+    CELLM_RUN(head_product_mma_kernel, grid, 128, smem, stream, (__nv_bfloat16*)out, ldo, out_hs, (const __nv_bfloat16*)in, ldi,
+              in_hs, (const __nv_bfloat16*)w, T, N, K);
     return CELLM_OK;
 }

@@ -1,6 +1,7 @@
 // A sublayer's result joins the residual stream through a gate and a norm:
 //
-//   v[t]  = m[t] * sigmoid(g[t] + b)          (the gate is optional: without it v = m)
+//   v[t]  = (m[t] + c) * sigmoid(g[t] + b)    (the gate is optional: without it v = m + c; so is c, a bias that the
+//                                              product behind m has not taken yet)
 //   x[t] += v[t] / rms_per_group(v[t]) * w    (the row in `groups` equal consecutive parts, each divided by its own
 //                                              sqrt(mean(part^2) + eps))
 //   y[t]  = x[t] in the activations' element type (optional: what the next sublayer's products read)
@@ -11,7 +12,7 @@
 #include "common.cuh"
 
 template <typename TA, typename TW>
-__global__ void gated_norm_add_kernel(float* __restrict__ x, const TA* __restrict__ m, const TA* __restrict__ gate,
+__global__ void gated_norm_add_kernel(float* __restrict__ x, const TA* __restrict__ m, const TW* __restrict__ m_bias, const TA* __restrict__ gate,
                                       const TW* __restrict__ gate_bias, const TW* __restrict__ w, TA* __restrict__ y,
                                       int H, int groups, float eps) {
     extern __shared__ float vals[];      // [H]
@@ -25,6 +26,7 @@ __global__ void gated_norm_add_kernel(float* __restrict__ x, const TA* __restric
         float ss = 0.f;
         for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
             float v = to_float(m[row + i]);
+            if (m_bias) v += to_float(m_bias[i]);
             if (gate) {
                 float z = to_float(gate[row + i]);
                 if (gate_bias) z += to_float(gate_bias[i]);
@@ -47,6 +49,7 @@ __global__ void gated_norm_add_kernel(float* __restrict__ x, const TA* __restric
 // per (row, group), every thread keeps its 8 values in registers, each element is read once and written once in
 // 16-byte pieces. The group's sum is taken in an order that depends on its length only.
 __global__ void gated_norm_add_vec8_kernel(float* __restrict__ x, const __nv_bfloat16* __restrict__ m,
+                                           const __nv_bfloat16* __restrict__ m_bias,
                                            const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ gate_bias,
                                            const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int H, int Hg,
                                            float eps) {
@@ -56,14 +59,20 @@ __global__ void gated_norm_add_vec8_kernel(float* __restrict__ x, const __nv_bfl
     const bool on = i0 < Hg;
     const int col = blockIdx.y * Hg + i0;
     const size_t at = (size_t)blockIdx.x * H + col;
-    float wv[8], bv[8];
+    float wv[8], bv[8], cv[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) wv[j] = bv[j] = 0.f;
+    for (int j = 0; j < 8; ++j) wv[j] = bv[j] = cv[j] = 0.f;
     if (on) {                                   // weights and bias are not the work of the kernel before this one
         const uint4 wq = *reinterpret_cast<const uint4*>(w + col);
         const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wq);
 #pragma unroll
         for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(wp[j]); wv[2 * j] = f.x; wv[2 * j + 1] = f.y; }
+        if (m_bias) {
+            const uint4 cq = *reinterpret_cast<const uint4*>(m_bias + col);
+            const __nv_bfloat162* cp = reinterpret_cast<const __nv_bfloat162*>(&cq);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(cp[j]); cv[2 * j] = f.x; cv[2 * j + 1] = f.y; }
+        }
         if (gate_bias) {
             const uint4 bq = *reinterpret_cast<const uint4*>(gate_bias + col);
             const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&bq);
@@ -79,7 +88,7 @@ __global__ void gated_norm_add_vec8_kernel(float* __restrict__ x, const __nv_bfl
         const uint4 mq = *reinterpret_cast<const uint4*>(m + at);
         const __nv_bfloat162* mp = reinterpret_cast<const __nv_bfloat162*>(&mq);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(mp[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(mp[j]); v[2 * j] = f.x + cv[2 * j]; v[2 * j + 1] = f.y + cv[2 * j + 1]; }
         if (gate) {
             const uint4 gq = *reinterpret_cast<const uint4*>(gate + at);
             const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gq);
@@ -115,19 +124,19 @@ __global__ void gated_norm_add_vec8_kernel(float* __restrict__ x, const __nv_bfl
     }
 }
 
-// x: [T, H] float, updated in place; m, gate: [T, H] of the activations' type (gate may be null); gate_bias, w: [H] of the
-// weights' type (gate_bias may be null); y: [T, H] of the activations' type or null.
-CELLM_API int cellm_gated_norm_add(float* x, const void* m, const void* gate, const void* gate_bias, const void* w, int w_dtype,
+// x: [T, H] float, updated in place; m, gate: [T, H] of the activations' type (gate may be null); m_bias, gate_bias, w: [H] of
+// the weights' type (the biases may be null); y: [T, H] of the activations' type or null.
+CELLM_API int cellm_gated_norm_add(float* x, const void* m, const void* m_bias, const void* gate, const void* gate_bias, const void* w, int w_dtype,
                                    void* y, int T, int H, int groups, float eps, int act_dtype, cudaStream_t stream) {
     if (T <= 0) return CELLM_OK;
     if (groups < 1 || H % groups || H <= 0) return CELLM_ERR_SIZE;
     if (!x || !m || !w) return CELLM_ERR_ARG;
     const int Hg = H / groups;
     if (act_dtype == CELLM_BF16 && w_dtype == CELLM_BF16 && (Hg & 7) == 0 && Hg <= 8192 &&
-        (((uintptr_t)x | (uintptr_t)m | (uintptr_t)gate | (uintptr_t)gate_bias | (uintptr_t)w | (uintptr_t)y) & 15) == 0) {
+        (((uintptr_t)x | (uintptr_t)m | (uintptr_t)m_bias | (uintptr_t)gate | (uintptr_t)gate_bias | (uintptr_t)w | (uintptr_t)y) & 15) == 0) {
         const int vthreads = ((Hg / 8 + 31) / 32) * 32;
         CELLM_RUN(gated_norm_add_vec8_kernel, dim3((unsigned)T, (unsigned)groups), vthreads, 0, stream, x, (const __nv_bfloat16*)m,
-                  (const __nv_bfloat16*)gate, (const __nv_bfloat16*)gate_bias, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, Hg, eps);
+                  (const __nv_bfloat16*)m_bias, (const __nv_bfloat16*)gate, (const __nv_bfloat16*)gate_bias, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, Hg, eps);
         return CELLM_OK;
     }
     const size_t smem = (size_t)H * sizeof(float);
@@ -137,7 +146,7 @@ CELLM_API int cellm_gated_norm_add(float* x, const void* m, const void* gate, co
 #define LAUNCH(TA, TW)                                                                                                 \
     do {                                                                                                               \
         if (smem > 48 * 1024) cudaFuncSetAttribute(gated_norm_add_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        CELLM_RUN((gated_norm_add_kernel<TA, TW>), T, threads, smem, stream, x, (const TA*)m, (const TA*)gate,          \
+        CELLM_RUN((gated_norm_add_kernel<TA, TW>), T, threads, smem, stream, x, (const TA*)m, (const TW*)m_bias, (const TA*)gate, \
                   (const TW*)gate_bias, (const TW*)w, (TA*)y, H, groups, eps);                                          \
     } while (0)
     if (act_dtype == CELLM_F32 && w_dtype == CELLM_F32) LAUNCH(float, float);

@@ -38,7 +38,7 @@ typedef int (*GemmConvFn)(P y, CP a, CP wt, int M, int Nt, int K, i64 lda, i64 l
 typedef int (*GemmRopeFn)(P q, CP a, CP w, int M, int K, i64 lda, i64 ldw, int bn, int split_k, CP q_w, CP k_w, float eps,
                           CP positions, CP bt, int bt_stride, P kp, P vp, int pages, int page_size, int nh, int nkv, CP inv_freq,
                           int w_is_static, P err, P stream);
-typedef int (*GatedNormAddFn)(P x, CP m, CP gate, CP gate_bias, CP w, int w_tag, P y, int T, int H, int groups, float eps, int act_tag,
+typedef int (*GatedNormAddFn)(P x, CP m, CP m_bias, CP gate, CP gate_bias, CP w, int w_tag, P y, int T, int H, int groups, float eps, int act_tag,
                               P stream);
 typedef int (*StreamCastFn)(P y, CP x, i64 n, int act_tag, P stream);
 typedef int (*MinGruScanFn)(P out, CP proj, i64 ld, int proj_tag, CP bz, CP bx, int w_tag, P state, i64 slot_stride, CP slot_ids, CP cu,
@@ -49,6 +49,7 @@ typedef int (*LatentPrepFn)(P q_plain, P q_full, CP proj, i64 ld, int proj_tag, 
 typedef int (*HeadProductFn)(P out, i64 ldo, i64 out_hs, CP in, i64 ldi, i64 in_hs, CP w, int T, int heads, int N, int K, int tag, P stream);
 typedef int (*GatedActFn)(P h, CP gu, CP bg, CP bu, int w_tag, int T, int ff, int act, int tag, int gu_tag, P stream);
 typedef int (*BiasAddFn)(P out, CP in, CP b, int w_tag, int T, int N, int tag, P stream);
+typedef int (*HeadProductMmaFn)(P out, i64 ldo, i64 out_hs, CP in, i64 ldi, i64 in_hs, CP w, int T, int heads, int N, int K, P stream);
 typedef int (*AttentionLatentFn)(P out, P part_o, P part_ml, CP q, CP pool, CP cu, CP ctx, CP bt, int bt_stride, int B, int T, int n_tiles,
                                  int pages, int page_size, int nh, int kw, int dv, float scale, int nsplit, P err, P stream);
 
@@ -99,6 +100,10 @@ struct Run {
     // layers whose sublayers read the stream itself: the stream in the activations' type, and whether y holds it now
     void* stream_copy = nullptr;
     bool stream_in_y = false;
+    // a bias that the pending result has not taken yet (the gate-and-norm kernel right behind it adds it), and whether
+    // the record that runs now may leave its bias so
+    const void* pending_bias = nullptr;
+    bool may_leave_bias = false;
 
     ExecFn last_fn = FN_COUNT;
     template <typename F> F fn(ExecFn which) {
@@ -158,13 +163,18 @@ struct Run {
         }
     }
     // out[t, h * out_hs + n] = sum_k in[t, h * in_hs + k] * w[h][n][k] for per-head matrices w [heads, N, K]: many tokens
-    // under bfloat16 run the tensor-core product once a head (operands where TMA can fetch them: 16-byte rows), the
-    // rest one kernel over all heads
+    // under bfloat16 run on the tensor cores, all heads in one launch where K fits two tiles in shared memory (else the
+    // tcgen05 product once a head); the rest one plain kernel over all heads
     void head_products(void* out, i64 ldo, i64 out_hs, const void* in, i64 ldi, i64 in_hs, const void* w, i64 T, i64 heads, i64 N,
                        i64 K) {
-        const bool tc = act == EXEC_BF16 && T >= 128 && K % 8 == 0 && ldi % 8 == 0 && in_hs % 8 == 0 && (N * K) % 8 == 0 &&
+        const bool tc = act == EXEC_BF16 && T > 16 && K % 8 == 0 && ldi % 8 == 0 && in_hs % 8 == 0 && (N * K) % 8 == 0 &&
                         ((uintptr_t)in % 16) == 0 && ((uintptr_t)w % 16) == 0;
-        if (!tc) {
+        if (tc && K % 16 == 0 && K <= 512) {
+            LAUNCH(fn<HeadProductMmaFn>(FN_HEAD_PRODUCT_MMA)(out, ldo, out_hs, in, ldi, in_hs, w, (int)T, (int)heads, (int)N, (int)K, s.stream),
+                   "head_product_mma");
+            return;
+        }
+        if (!tc || T < 128) {
             LAUNCH(fn<HeadProductFn>(FN_HEAD_PRODUCT)(out, ldo, out_hs, in, ldi, in_hs, w, (int)T, (int)heads, (int)N, (int)K, (int)act,
                                                   s.stream),
                    "head_product");
@@ -263,7 +273,9 @@ struct Run {
         if (n.gate.w) g = linear(input(), n.gate, T, H, act);
         // without a copy of the stream yet (no sublayer of this pass has read the stream so far) y is left to the next reader
         void* y = act != EXEC_F32 ? stream_copy : nullptr;
-        LAUNCH(fn<GatedNormAddFn>(FN_GATED_NORM_ADD)(regs.x, regs.pending, g, n.gate_bias, n.w, (int)n.w_dtype, y, (int)T, (int)H,
+        const void* m_bias = pending_bias;
+        pending_bias = nullptr;
+        LAUNCH(fn<GatedNormAddFn>(FN_GATED_NORM_ADD)(regs.x, regs.pending, m_bias, g, n.gate_bias, n.w, (int)n.w_dtype, y, (int)T, (int)H,
                                                  (int)std::max<i64>(n.groups, 1), (float)n.eps, (int)act, s.stream),
            "gated_norm_add");
         regs.pending = nullptr;
@@ -335,7 +347,17 @@ struct Run {
         }
     }
     void run(const ExecOps& ops) {
-        for (i64 i = 0; i < ops.n; ++i) run(ops.ops[i]);
+        for (i64 i = 0; i < ops.n; ++i) {
+            // a feed-forward whose result goes straight into a gate-and-norm kernel leaves its last bias to that kernel
+            may_leave_bias = false;
+            if (ops.ops[i].kind == OP_GATED_MLP && i + 1 < ops.n && ops.ops[i + 1].kind == OP_GATED_NORM_ADD) {
+                const GatedMlpParams& f = *static_cast<const GatedMlpParams*>(ops.ops[i].params);
+                const GatedNormAddParams& n = *static_cast<const GatedNormAddParams*>(ops.ops[i + 1].params);
+                may_leave_bias = f.b_dtype == n.w_dtype;
+            }
+            run(ops.ops[i]);
+        }
+        may_leave_bias = false;
     }
 };
 
@@ -580,7 +602,10 @@ void Run::gated_mlp(const GatedMlpParams& L, const void* x, void* out) {
     void* h = arena.take(T * L.ff * elt(act));
     LAUNCH(fn<GatedActFn>(FN_GATED_ACT)(h, gu, L.bg, L.bu, (int)L.b_dtype, (int)T, (int)L.ff, (int)L.act, (int)act, (int)EXEC_F32, s.stream),
            "gated_act");
-    if (L.bd) {
+    if (L.bd && may_leave_bias) {
+        product(out, h, L.down, T, L.ff, act);
+        pending_bias = L.bd;
+    } else if (L.bd) {
         void* sums = linear(h, L.down, T, L.ff, EXEC_F32);
         LAUNCH(fn<BiasAddFn>(FN_BIAS_ADD)(out, sums, L.bd, (int)L.b_dtype, (int)T, (int)L.down.N, (int)act, s.stream), "bias_add");
     } else {
@@ -591,11 +616,11 @@ void Run::gated_mlp(const GatedMlpParams& L, const void* x, void* out) {
 void Run::mingru(const MinGruParams& L, const ExecItem& it, const void* x, void* out) {
     const i64 T = s.T, H = p.H, W = L.width;
     if (!it.state) throw std::runtime_error("executor: a recurrent mixer without a state slot");
-    // the three projections side by side, in the activations' type like every product's output; gates, candidate and
-    // state are formed from them in 32-bit
-    void* proj = linear(x, L.in_proj, T, H, act);
+    // the three projections side by side as 32-bit sums: what enters the recurrence is formed from them unrounded (a
+    // rounding of z would be carried along by the state)
+    void* proj = linear(x, L.in_proj, T, H, EXEC_F32);
     void* y = arena.take(T * W * elt(act));
-    LAUNCH(fn<MinGruScanFn>(FN_MINGRU_SCAN)(y, proj, 3 * W, (int)act, L.bz, L.bx, (int)L.b_dtype, it.state, it.slot_stride, s.slot_ids,
+    LAUNCH(fn<MinGruScanFn>(FN_MINGRU_SCAN)(y, proj, 3 * W, (int)EXEC_F32, L.bz, L.bx, (int)L.b_dtype, it.state, it.slot_stride, s.slot_ids,
                                         s.cu_seqlens, (int)T, (int)s.B, (int)W, (int)it.n_slots, (int)s.max_q_len, (int)act, s.err, s.stream),
            "mingru_scan");
     product(out, y, L.out_proj, T, W, act);

@@ -122,7 +122,7 @@ typedef i64 (*PythonOpFn)(i64 token, ExecRegs* regs);
 enum ExecFn {
     FN_EMBED, FN_ADD_RMSNORM, FN_RESIDUAL_ADD, FN_SWIGLU, FN_SHORT_CONV, FN_QK_NORM_ROPE, FN_ATTENTION_PLAIN, FN_GEMM_PLAIN,
     FN_ATTENTION_DECODE, FN_ATTENTION_TC, FN_ATTENTION_FLASH, FN_GEMM_TCGEN05, FN_GEMM_CONV, FN_GEMM_ROPE,
-    FN_GATED_NORM_ADD, FN_STREAM_CAST, FN_MINGRU_SCAN, FN_LATENT_PREP, FN_HEAD_PRODUCT, FN_GATED_ACT, FN_BIAS_ADD, FN_ATTENTION_LATENT, FN_COUNT
+    FN_GATED_NORM_ADD, FN_STREAM_CAST, FN_MINGRU_SCAN, FN_LATENT_PREP, FN_HEAD_PRODUCT, FN_GATED_ACT, FN_BIAS_ADD, FN_ATTENTION_LATENT, FN_HEAD_PRODUCT_MMA, FN_COUNT
 };
 
 struct ExecProgram {

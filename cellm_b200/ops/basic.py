@@ -207,17 +207,18 @@ def stream_cast(x: torch.Tensor, act_dtype: torch.dtype) -> torch.Tensor:
 
 
 def gated_norm_add(x: torch.Tensor, m: torch.Tensor, gate: Optional[torch.Tensor], gate_bias: Optional[torch.Tensor],
-                   w: torch.Tensor, groups: int, eps: float, want_copy: bool = True) -> Optional[torch.Tensor]:
-    """x [T, H] float32 += group_rms_norm(m * sigmoid(gate + gate_bias)) * w, in place (gate None: no gate). m and gate
-    are of the activations' type. Returns the new stream in that type (x itself for float32), or None if not wanted."""
-    require_cuda(x, m, gate, gate_bias, w)
+                   w: torch.Tensor, groups: int, eps: float, want_copy: bool = True,
+                   m_bias: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """x [T, H] float32 += group_rms_norm((m + m_bias) * sigmoid(gate + gate_bias)) * w, in place (gate None: no gate;
+    m_bias None: none). m and gate are of the activations' type, the biases of w's. Returns the new stream in that type (x itself for float32), or None if not wanted."""
+    require_cuda(x, m, gate, gate_bias, w, m_bias)
     T, H = x.shape
     if x.dtype != torch.float32 or m.shape != x.shape or (gate is not None and (gate.shape != x.shape or gate.dtype != m.dtype)):
         raise ValueError("gated_norm_add: x float32 [T, H]; m and gate [T, H] of one element type")
-    if w.numel() != H or (gate_bias is not None and (gate_bias.numel() != H or gate_bias.dtype != w.dtype)):
+    if w.numel() != H or any(b is not None and (b.numel() != H or b.dtype != w.dtype) for b in (gate_bias, m_bias)):
         raise ValueError("gated_norm_add: w and gate_bias have H values of one element type")
     y = torch.empty_like(m) if (want_copy and m.dtype != torch.float32) else None
-    check(fn(_LIB, "cellm_gated_norm_add")(ptr(x), ptr(m), ptr(gate), ptr(gate_bias), ptr(w), tag(w), ptr(y), T, H, int(groups),
+    check(fn(_LIB, "cellm_gated_norm_add")(ptr(x), ptr(m), ptr(m_bias), ptr(gate), ptr(gate_bias), ptr(w), tag(w), ptr(y), T, H, int(groups),
                                            float(eps), tag(m), stream_of(x)), "gated_norm_add")
     return y if y is not None else (x if want_copy else None)
 

@@ -109,7 +109,7 @@ ENTRY_POINTS = [("kernels_common", "cellm_embed"), ("kernels_common", "cellm_add
                 ("kernels_common", "cellm_gated_norm_add"), ("kernels_common", "cellm_stream_cast"),
                 ("kernels_common", "cellm_mingru_scan"), ("kernels_common", "cellm_latent_prep"),
                 ("kernels_common", "cellm_head_product"), ("kernels_common", "cellm_gated_act"), ("kernels_common", "cellm_bias_add"),
-                ("attention_latent", "cellm_attention_latent")]
+                ("attention_latent", "cellm_attention_latent"), ("attention_latent", "cellm_head_product_mma")]
 # libraries a model whose activations are 32-bit never calls into (they need not be compiled for it)
 BF16_ONLY_LIBRARIES = ("attention_decode", "attention_tc", "attention_flash", "gemm_tcgen05", "attention_latent")
 # libraries that only records of these kinds reach (a program without such a record need not have them compiled)

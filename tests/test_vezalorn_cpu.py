@@ -95,15 +95,16 @@ def test_decode_step_kernels(monkeypatch):
         "gemm_tcgen05", "gated_norm_add",                                        # the gate's product, gate + norm + sum
         "gemm_tcgen05", "latent_prep", "head_product", "attention_latent", "head_product", "gemm_tcgen05",
         "gemm_tcgen05", "gated_norm_add",
-        "gemm_tcgen05", "gated_act", "gemm_tcgen05", "bias_add",                 # gate | up, activation, the way back and its bias
-        "gemm_tcgen05", "gated_norm_add",
+        "gemm_tcgen05", "gated_act", "gemm_tcgen05",                             # gate | up, activation, the way back
+        "gemm_tcgen05", "gated_norm_add",                                        # (its bias is added by the gate-and-norm kernel)
         "add_rmsnorm", "gemm_tcgen05"]
     prep = rec.of("cellm_latent_prep")[0]
     assert prep[15:22] == (3, 4, 32, 16, 64, 16, prep[21]) and prep[12] is not None          # tokens, heads, dim, rot_dim, rank, rot; a cache to write
     att = rec.of("cellm_attention_latent")[0]
     assert (att[9], att[10], att[14], att[15], att[16]) == (3, 3, 4, 80, 64)                 # requests, tokens, heads, row width, value width
     norm = rec.of("cellm_gated_norm_add")[0]
-    assert (norm[7], norm[8], norm[9]) == (3, 128, 2) and norm[2] is not None and norm[6] is not None
+    assert (norm[8], norm[9], norm[10]) == (3, 128, 2) and norm[3] is not None and norm[7] is not None and norm[2] is None
+    assert rec.of("cellm_gated_norm_add")[2][2] is not None                                   # the feed-forward's last bias
     final = rec.of("cellm_add_rmsnorm")[0]
     assert final[8] == 2                                                                      # the model's norm is in groups too
     assert rec.of("cellm_embed")[0][7] == 3.0
@@ -128,9 +129,9 @@ def test_prompt_step_kernels(monkeypatch):
     run_step(model, plan, [600], [0])
     scan = rec.of("cellm_mingru_scan")[0]
     assert scan[11:16] == (600, 1, 192, scan[14], 600)
-    assert "head_product" not in names_of(rec)                      # 2 x 4 heads as tensor-core products of their own
-    per_head = [g for g in rec.of("cellm_gemm_tcgen05") if (g[4], g[5]) in ((64, 32), (48, 64))]
-    assert len(per_head) == 8 and {g[8] for g in per_head} == {4 * 80, 4 * 48}                # written at the heads' pitch
+    assert "head_product" not in names_of(rec)                      # all heads in one tensor-core launch, twice
+    per_head = rec.of("cellm_head_product_mma")
+    assert [(g[1], g[2], g[7], g[8], g[9], g[10]) for g in per_head] == [(4 * 80, 80, 600, 4, 64, 32), (4 * 48, 48, 600, 4, 48, 64)]
     att = rec.of("cellm_attention_latent")[0]
     # 38 tiles leave most of 148 SMs idle: the keys in pieces (two CTAs an SM wanted, at least two blocks of keys a piece)
     assert att[11] == (600 * 4 + 63) // 64 and att[18] == 5 and att[1] is not None

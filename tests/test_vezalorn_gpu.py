@@ -64,7 +64,9 @@ PAGE = {"a": 8, "b": 16, "c": 16}
 
 def write_model(folder, config, seed, dtype="bfloat16", init=None):
     from cellm_b200.weights import InitSpec, write_random_model
-    init = init or InitSpec(linear_std=0.12, embedding_std=0.08, bias_std=0.1, norm_jitter=0.2)
+    # matrices five times as large as a trained model's 0.02, so that a wrong key or a stale state moves the logits; larger
+    # ones make gates and softmax so steep that bfloat16's own rounding of their inputs comes near the bound of the comparison
+    init = init or InitSpec(linear_std=0.1, embedding_std=0.08, bias_std=0.1, norm_jitter=0.2)
     return write_random_model(str(folder), config, seed, dtype, init)
 
 
@@ -247,10 +249,13 @@ def test_gated_norm_add(dtype, H, groups, gate):
     m, z = _t(torch.randn(T, H, generator=g) * 3, dtype), _t(torch.randn(T, H, generator=g) * 2, dtype)
     b, w = _t(torch.randn(H, generator=g), dtype), _t(1 + 0.3 * torch.randn(H, generator=g), dtype)
     md, zd, bd, wd = (v.cpu().double() for v in (m, z, b, w))
+    c = _t(torch.randn(H, generator=g), dtype) if H == 96 else None          # a bias the result has not taken yet
+    if c is not None:
+        md = md + c.cpu().double()
     v = md * torch.sigmoid(zd + bd) if gate else md
     want = x.double() + plain.group_rms_norm(v, wd, groups, 1e-5)
     xd = x.to(DEV)
-    y = ops.gated_norm_add(xd, m, z if gate else None, b if gate else None, w, groups, 1e-5)
+    y = ops.gated_norm_add(xd, m, z if gate else None, b if gate else None, w, groups, 1e-5, m_bias=c)
     torch.testing.assert_close(xd.cpu().double(), want, rtol=1e-5, atol=1e-5)
     torch.testing.assert_close(y.cpu().double(), want.to(dtype).double(), rtol=1e-2 if dtype == torch.bfloat16 else 1e-5, atol=1e-5)
 
