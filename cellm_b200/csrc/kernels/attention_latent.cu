@@ -100,6 +100,7 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
         cp_async_wait<1>();
         __syncthreads();
         const __nv_bfloat16* ks_ = k_s + stage * BN * stride;
+        if (r0 + rw * 16 < rows) {           // (a decoded token's heads fill one or two of the four row groups)
         float s[BN / 8][4];
 #pragma unroll
         for (int n = 0; n < BN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
@@ -169,6 +170,7 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                 mma_bf16(o[2 * n2 + 1], pf[kk], vf[2], vf[3]);
             }
         }
+        }
         __syncthreads();
     }
     cp_async_wait<0>();
@@ -213,35 +215,28 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
 // The pieces of a row merged in their order: out = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s.
 __global__ void latent_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
                                     const float* __restrict__ part_ml, size_t n_rows, int dv, int nsplit) {
-    extern __shared__ float wt[];        // [nsplit] weight of each piece, already divided by the whole sum
+    extern __shared__ float ml[];        // [nsplit][2]: maximum and sum of each piece, then its weight in [s][0]
     pdl_trigger();
     pdl_wait();
     const size_t r = blockIdx.x;
-    if (threadIdx.x < 32) {
-        float M = -INFINITY;
-        for (int s = threadIdx.x; s < nsplit; s += 32) M = fmaxf(M, part_ml[((size_t)s * n_rows + r) * 2]);
-        M = warp_max(M);
-        float L = 0.f;
-        for (int s0 = 0; s0 < nsplit; s0 += 32) {          // the pieces' sums in their order
-            const int s = s0 + threadIdx.x;
-            float e = 0.f, l = 0.f;
-            if (s < nsplit) {
-                const float m = part_ml[((size_t)s * n_rows + r) * 2];
-                e = m == -INFINITY ? 0.f : fast_exp2(m - M);
-                l = e * part_ml[((size_t)s * n_rows + r) * 2 + 1];
-                wt[s] = e;
-            }
-            L += warp_sum(l);
-        }
-        __syncwarp();
-        const float inv = L > 0.f ? 1.0f / L : 0.f;
-        for (int s = threadIdx.x; s < nsplit; s += 32) wt[s] *= inv;
+    for (int s = threadIdx.x; s < nsplit; s += blockDim.x) {
+        const float2 v = *reinterpret_cast<const float2*>(part_ml + ((size_t)s * n_rows + r) * 2);
+        ml[2 * s] = v.x;
+        ml[2 * s + 1] = v.y;
     }
     __syncthreads();
+    float M = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ml[2 * s]);
+    float L = 0.f;
+    for (int s = 0; s < nsplit; ++s) L += ml[2 * s] == -INFINITY ? 0.f : fast_exp2(ml[2 * s] - M) * ml[2 * s + 1];   // in the pieces' order
+    const float inv = L > 0.f ? 1.0f / L : 0.f;
     for (int d = threadIdx.x; d < dv; d += blockDim.x) {
         float acc = 0.f;
-#pragma unroll 4
-        for (int s = 0; s < nsplit; ++s) acc = fmaf(wt[s], part_o[((size_t)s * n_rows + r) * dv + d], acc);
+#pragma unroll 8
+        for (int s = 0; s < nsplit; ++s) {
+            const float wgt = ml[2 * s] == -INFINITY ? 0.f : fast_exp2(ml[2 * s] - M) * inv;
+            acc = fmaf(wgt, part_o[((size_t)s * n_rows + r) * dv + d], acc);
+        }
         out[r * dv + d] = __float2bfloat16_rn(acc);
     }
 }
@@ -357,7 +352,7 @@ CELLM_API int cellm_attention_latent(void* out, float* part_o, float* part_ml, c
     else LAUNCH(16, 32, 1024);
 #undef LAUNCH
     if (nsplit > 1)
-        CELLM_RUN(latent_merge_kernel, (unsigned)((size_t)T * nh), dv >= 256 ? 256 : (dv >= 128 ? 128 : 64), (size_t)nsplit * sizeof(float), stream, (__nv_bfloat16*)out, part_o,
+        CELLM_RUN(latent_merge_kernel, (unsigned)((size_t)T * nh), dv >= 256 ? 256 : (dv >= 128 ? 128 : 64), (size_t)nsplit * 2 * sizeof(float), stream, (__nv_bfloat16*)out, part_o,
                   part_ml, (size_t)T * nh, dv, nsplit);
     return CELLM_OK;
 }

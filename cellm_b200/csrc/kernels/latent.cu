@@ -178,39 +178,31 @@ head_product_kernel(TA* __restrict__ out, long long ldo, long long out_hs, const
 }
 
 // A few tokens (decoding, bfloat16): the matrices are what has to be read, once. A block takes 16 output rows of one
-// head; the tokens' inputs wait in shared memory as floats; eight neighbouring threads share a row, each over an eighth
-// of K in 16-byte loads, and add their sums by three shuffles. K (a multiple of 64) is summed in the same order for every
-// token count up to HP_SMALL_T.
+// head; the tokens' inputs wait in shared memory; eight neighbouring threads share a row and take neighbouring 16-byte
+// pieces of it by turns (so a row's loads are whole 128-byte lines and the inputs' reads fall into different banks),
+// and add their sums by three shuffles. K (a multiple of 64) is summed in the same order for every token count up to
+// HP_SMALL_T.
 #define HP_SMALL_T 16
 __global__ void __launch_bounds__(128)
 head_product_small_kernel(__nv_bfloat16* __restrict__ out, long long ldo, long long out_hs, const __nv_bfloat16* __restrict__ in,
                           long long ldi, long long in_hs, const __nv_bfloat16* __restrict__ w, int T, int N, int K, int vec_in) {
-    extern __shared__ float xin[];       // [T][K]
+    extern __shared__ __align__(16) __nv_bfloat16 xin[];       // [T][K]
     pdl_trigger();
     const int h = blockIdx.y;
     const int n = blockIdx.x * 16 + (threadIdx.x >> 3), kq = threadIdx.x & 7;
-    const int kn = K / 8;
     const bool on = n < N;
-    const __nv_bfloat16* wr = w + ((size_t)h * N + (on ? n : 0)) * K + kq * kn;
+    const __nv_bfloat16* wr = w + ((size_t)h * N + (on ? n : 0)) * K;
     pdl_wait();
     if (vec_in) {                        // the inputs' rows start on 16-byte borders: eight values a load
         const int K8 = K / 8;
-#pragma unroll 4
         for (int i = threadIdx.x; i < T * K8; i += blockDim.x) {
             const int t = i / K8, k = (i - t * K8) * 8;
-            const uint4 q = *reinterpret_cast<const uint4*>(in + (size_t)t * ldi + h * in_hs + k);
-            const __nv_bfloat162* qp = reinterpret_cast<const __nv_bfloat162*>(&q);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 f = __bfloat1622float2(qp[j]);
-                xin[t * K + k + 2 * j] = f.x;
-                xin[t * K + k + 2 * j + 1] = f.y;
-            }
+            *reinterpret_cast<uint4*>(xin + t * K + k) = *reinterpret_cast<const uint4*>(in + (size_t)t * ldi + h * in_hs + k);
         }
     } else {
         for (int i = threadIdx.x; i < T * K; i += blockDim.x) {
             const int t = i / K, k = i - t * K;
-            xin[i] = __bfloat162float(in[(size_t)t * ldi + h * in_hs + k]);
+            xin[i] = in[(size_t)t * ldi + h * in_hs + k];
         }
     }
     __syncthreads();
@@ -218,18 +210,23 @@ head_product_small_kernel(__nv_bfloat16* __restrict__ out, long long ldo, long l
 #pragma unroll
     for (int t = 0; t < HP_SMALL_T; ++t) acc[t] = 0.f;
 #pragma unroll 2
-    for (int k0 = 0; k0 < kn; k0 += 8) {
+    for (int k0 = kq * 8; k0 < K; k0 += 64) {
         const uint4 wq = *reinterpret_cast<const uint4*>(wr + k0);
         const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wq);
         float wv[8];
 #pragma unroll
         for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(wp[j]); wv[2 * j] = f.x; wv[2 * j + 1] = f.y; }
-        const float* xr = xin + kq * kn + k0;
 #pragma unroll
         for (int t = 0; t < HP_SMALL_T; ++t) {
             if (t < T) {
+                const uint4 xq = *reinterpret_cast<const uint4*>(xin + t * K + k0);
+                const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xq);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[t] = fmaf(xr[t * K + j], wv[j], acc[t]);
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __bfloat1622float2(xp[j]);
+                    acc[t] = fmaf(f.x, wv[2 * j], acc[t]);
+                    acc[t] = fmaf(f.y, wv[2 * j + 1], acc[t]);
+                }
             }
         }
     }
@@ -251,10 +248,10 @@ CELLM_API int cellm_head_product(void* out, long long ldo, long long out_hs, con
     if (T <= 0 || heads <= 0 || N <= 0) return CELLM_OK;
     if (K <= 0) return CELLM_ERR_SIZE;
     // (32-bit activations always take the tiles below: one order of the sums whatever the number of tokens)
-    if (dtype == CELLM_BF16 && T <= HP_SMALL_T && (size_t)T * K * sizeof(float) <= 48 * 1024 && (K & 63) == 0 &&
+    if (dtype == CELLM_BF16 && T <= HP_SMALL_T && (size_t)T * K * 2 <= 48 * 1024 && (K & 63) == 0 &&
         ((uintptr_t)w & 15) == 0) {
         const dim3 sgrid((unsigned)((N + 15) / 16), (unsigned)heads);
-        const size_t smem = (size_t)T * K * sizeof(float);
+        const size_t smem = (size_t)T * K * 2;
         CELLM_RUN(head_product_small_kernel, sgrid, 128, smem, stream, (__nv_bfloat16*)out, ldo, out_hs,
                   (const __nv_bfloat16*)in, ldi, in_hs, (const __nv_bfloat16*)w, T, N, K,
                   (int)((((uintptr_t)in & 15) == 0) && (ldi & 7) == 0 && (in_hs & 7) == 0));
