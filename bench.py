@@ -236,9 +236,10 @@ def matrix_bytes(model) -> int:
     def scan(obj, depth=0):
         nonlocal total
         if isinstance(obj, torch.Tensor):
-            if obj.dim() >= 2 and obj.data_ptr() not in seen:
-                seen.add(obj.data_ptr())
-                total += obj.numel() * obj.element_size()
+            base = obj.untyped_storage().data_ptr()          # a view of rows of a matrix already counted is no new matrix
+            if obj.dim() >= 2 and base not in seen:
+                seen.add(base)
+                total += obj.untyped_storage().nbytes()
         elif isinstance(obj, dict):
             for v in obj.values():
                 scan(v, depth + 1)
@@ -247,7 +248,7 @@ def matrix_bytes(model) -> int:
                 scan(v, depth + 1)
         elif depth < 4 and hasattr(obj, "__dict__"):
             for k, v in vars(obj).items():
-                if k not in ("in_proj_tiled", "q_only", "_record", "_attend"):
+                if k not in ("in_proj_tiled", "q_only", "_record", "_attend", "stacked_view"):
                     scan(v, depth + 1)
     for blk in model.blocks:
         scan(blk)

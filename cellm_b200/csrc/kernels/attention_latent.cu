@@ -106,7 +106,7 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
         for (int n = 0; n < BN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
         const __nv_bfloat16* q_row = q_s + (rw * 16 + (lane & 15)) * stride + (lane >> 4) * 8;
         const __nv_bfloat16* k_row = ks_ + ((lane & 7) + ((lane >> 4) << 3)) * stride + ((lane >> 3) & 1) * 8;
-#pragma unroll 2
+#pragma unroll 4
         for (int k0 = 0; k0 < kw; k0 += 16) {
             uint32_t qf[4];
             ldmatrix_x4(qf, q_row + k0);

@@ -36,7 +36,7 @@ CELLM_API int cellm_swiglu(void* h, const void* gu, int T, int ff, int dtype, in
 // u = gu[t, ff + j]; act is silu (0) or the tanh form of gelu (1): 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
 // The biases may be absent. 32-bit math.
 template <typename T, typename TI, typename TW>
-__global__ void gated_act_kernel(T* __restrict__ h, const TI* __restrict__ gu, const TW* __restrict__ bg,
+__global__ void gated_act_kernel(T* __restrict__ h, const TI* __restrict__ gu, long long ld, const TW* __restrict__ bg,
                                  const TW* __restrict__ bu, int ff, int act, size_t n) {
     pdl_trigger();
     pdl_wait();
@@ -44,8 +44,8 @@ __global__ void gated_act_kernel(T* __restrict__ h, const TI* __restrict__ gu, c
     if (i >= n) return;
     const size_t t = i / ff;
     const int j = (int)(i - t * ff);
-    float g = to_float(gu[t * 2 * ff + j]);
-    float u = to_float(gu[t * 2 * ff + ff + j]);
+    float g = to_float(gu[t * ld + j]);
+    float u = to_float(gu[t * ld + ff + j]);
     if (bg) g += to_float(bg[j]);
     if (bu) u += to_float(bu[j]);
     float a;
@@ -56,7 +56,7 @@ __global__ void gated_act_kernel(T* __restrict__ h, const TI* __restrict__ gu, c
 
 // The same, four neighbouring outputs a thread in 16-byte loads of 32-bit gate and up (ff a multiple of 4).
 template <typename T, typename TW>
-__global__ void gated_act_vec4_kernel(T* __restrict__ h, const float* __restrict__ gu, const TW* __restrict__ bg,
+__global__ void gated_act_vec4_kernel(T* __restrict__ h, const float* __restrict__ gu, long long ld, const TW* __restrict__ bg,
                                       const TW* __restrict__ bu, int ff, int act, size_t n4) {
     pdl_trigger();
     pdl_wait();
@@ -65,8 +65,8 @@ __global__ void gated_act_vec4_kernel(T* __restrict__ h, const float* __restrict
     const size_t i = i4 * 4;
     const size_t t = i / ff;
     const int j = (int)(i - t * ff);
-    const float4 gq = *reinterpret_cast<const float4*>(gu + t * 2 * ff + j);
-    const float4 uq = *reinterpret_cast<const float4*>(gu + t * 2 * ff + ff + j);
+    const float4 gq = *reinterpret_cast<const float4*>(gu + t * ld + j);
+    const float4 uq = *reinterpret_cast<const float4*>(gu + t * ld + ff + j);
     float g[4] = {gq.x, gq.y, gq.z, gq.w}, u[4] = {uq.x, uq.y, uq.z, uq.w}, o[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -80,16 +80,17 @@ __global__ void gated_act_vec4_kernel(T* __restrict__ h, const float* __restrict
     for (int e = 0; e < 4; ++e) h[i + e] = from_float<T>(o[e]);
 }
 
-CELLM_API int cellm_gated_act(void* h, const void* gu, const void* bg, const void* bu, int w_dtype, int T, int ff, int act,
+CELLM_API int cellm_gated_act(void* h, const void* gu, long long ld, const void* bg, const void* bu, int w_dtype, int T, int ff, int act,
                               int dtype, int gu_dtype, cudaStream_t stream) {
     const size_t n = (size_t)T * ff;
     if (n == 0) return CELLM_OK;
     if (act != 0 && act != 1) return CELLM_ERR_ARG;
+    if (ld < 2LL * ff) return CELLM_ERR_SIZE;
     const int threads = 256;
-    if (gu_dtype == CELLM_F32 && (ff & 3) == 0 && ((uintptr_t)gu & 15) == 0) {
+    if (gu_dtype == CELLM_F32 && (ff & 3) == 0 && (ld & 3) == 0 && ((uintptr_t)gu & 15) == 0) {
         const size_t n4 = n / 4;
         const unsigned vblocks = (unsigned)((n4 + threads - 1) / threads);
-#define VEC(TT, TW) CELLM_RUN((gated_act_vec4_kernel<TT, TW>), vblocks, threads, 0, stream, (TT*)h, (const float*)gu, (const TW*)bg, (const TW*)bu, ff, act, n4)
+#define VEC(TT, TW) CELLM_RUN((gated_act_vec4_kernel<TT, TW>), vblocks, threads, 0, stream, (TT*)h, (const float*)gu, ld, (const TW*)bg, (const TW*)bu, ff, act, n4)
         if (dtype == CELLM_F32 && w_dtype == CELLM_F32) VEC(float, float);
         else if (dtype == CELLM_F32 && w_dtype == CELLM_BF16) VEC(float, __nv_bfloat16);
         else if (dtype == CELLM_BF16 && w_dtype == CELLM_BF16) VEC(__nv_bfloat16, __nv_bfloat16);
@@ -100,7 +101,7 @@ CELLM_API int cellm_gated_act(void* h, const void* gu, const void* bg, const voi
     }
     const unsigned blocks = (unsigned)((n + threads - 1) / threads);
 #define LAUNCH(TT, TI, TW) \
-    CELLM_RUN((gated_act_kernel<TT, TI, TW>), blocks, threads, 0, stream, (TT*)h, (const TI*)gu, (const TW*)bg, (const TW*)bu, ff, act, n)
+    CELLM_RUN((gated_act_kernel<TT, TI, TW>), blocks, threads, 0, stream, (TT*)h, (const TI*)gu, ld, (const TW*)bg, (const TW*)bu, ff, act, n)
     if (dtype == CELLM_F32 && gu_dtype == CELLM_F32 && w_dtype == CELLM_F32) LAUNCH(float, float, float);
     else if (dtype == CELLM_F32 && gu_dtype == CELLM_F32 && w_dtype == CELLM_BF16) LAUNCH(float, float, __nv_bfloat16);
     else if (dtype == CELLM_BF16 && gu_dtype == CELLM_F32 && w_dtype == CELLM_BF16) LAUNCH(__nv_bfloat16, float, __nv_bfloat16);

@@ -38,7 +38,7 @@ typedef int (*GemmConvFn)(P y, CP a, CP wt, int M, int Nt, int K, i64 lda, i64 l
 typedef int (*GemmRopeFn)(P q, CP a, CP w, int M, int K, i64 lda, i64 ldw, int bn, int split_k, CP q_w, CP k_w, float eps,
                           CP positions, CP bt, int bt_stride, P kp, P vp, int pages, int page_size, int nh, int nkv, CP inv_freq,
                           int w_is_static, P err, P stream);
-typedef int (*GatedNormAddFn)(P x, CP m, CP m_bias, CP gate, CP gate_bias, CP w, int w_tag, P y, int T, int H, int groups, float eps, int act_tag,
+typedef int (*GatedNormAddFn)(P x, CP m, CP m_bias, CP gate, i64 gate_ld, int gate_tag, CP gate_bias, CP w, int w_tag, P y, int T, int H, int groups, float eps, int act_tag,
                               P stream);
 typedef int (*StreamCastFn)(P y, CP x, i64 n, int act_tag, P stream);
 typedef int (*MinGruScanFn)(P out, CP proj, i64 ld, int proj_tag, CP bz, CP bx, int w_tag, P state, i64 slot_stride, CP slot_ids, CP cu,
@@ -47,7 +47,7 @@ typedef int (*LatentPrepFn)(P q_plain, P q_full, CP proj, i64 ld, int proj_tag, 
                             CP bt, int bt_stride, P pool, int pages, int page_size, int T, int heads, int dim, int rot_dim, int rank,
                             int rot, CP inv_freq, int act_tag, P err, P stream);
 typedef int (*HeadProductFn)(P out, i64 ldo, i64 out_hs, CP in, i64 ldi, i64 in_hs, CP w, int T, int heads, int N, int K, int tag, P stream);
-typedef int (*GatedActFn)(P h, CP gu, CP bg, CP bu, int w_tag, int T, int ff, int act, int tag, int gu_tag, P stream);
+typedef int (*GatedActFn)(P h, CP gu, i64 ld, CP bg, CP bu, int w_tag, int T, int ff, int act, int tag, int gu_tag, P stream);
 typedef int (*BiasAddFn)(P out, CP in, CP b, int w_tag, int T, int N, int tag, P stream);
 typedef int (*HeadProductMmaFn)(P out, i64 ldo, i64 out_hs, CP in, i64 ldi, i64 in_hs, CP w, int T, int heads, int N, int K, P stream);
 typedef int (*AttentionLatentFn)(P out, P part_o, P part_ml, CP q, CP pool, CP cu, CP ctx, CP bt, int bt_stride, int B, int T, int n_tiles,
@@ -104,6 +104,9 @@ struct Run {
     // the record that runs now may leave its bias so
     const void* pending_bias = nullptr;
     bool may_leave_bias = false;
+    // the gate's pre-activations where the sublayer's first product has formed them with its own (rows stacked behind its matrix)
+    const void* gate_at = nullptr;
+    i64 gate_ld = 0, gate_dtype = 0;
 
     ExecFn last_fn = FN_COUNT;
     template <typename F> F fn(ExecFn which) {
@@ -269,13 +272,20 @@ struct Run {
         if (!regs.pending) throw std::runtime_error("executor: a gate and norm without a sublayer's result before them");
         if (regs.phase != 1) throw std::runtime_error("executor: a gate and norm outside the layers");
         const i64 T = s.T, H = p.H;
-        void* g = nullptr;
-        if (n.gate.w) g = linear(input(), n.gate, T, H, act);
+        const void* g = nullptr;
+        i64 g_ld = H, g_dtype = act;
+        if (n.stacked) {
+            if (!gate_at) throw std::runtime_error("executor: a stacked gate whose sublayer left no gate");
+            g = gate_at, g_ld = gate_ld, g_dtype = gate_dtype;
+        } else if (n.gate.w) {
+            g = linear(input(), n.gate, T, H, act);
+        }
+        gate_at = nullptr;
         // without a copy of the stream yet (no sublayer of this pass has read the stream so far) y is left to the next reader
         void* y = act != EXEC_F32 ? stream_copy : nullptr;
         const void* m_bias = pending_bias;
         pending_bias = nullptr;
-        LAUNCH(fn<GatedNormAddFn>(FN_GATED_NORM_ADD)(regs.x, regs.pending, m_bias, g, n.gate_bias, n.w, (int)n.w_dtype, y, (int)T, (int)H,
+        LAUNCH(fn<GatedNormAddFn>(FN_GATED_NORM_ADD)(regs.x, regs.pending, m_bias, g, g_ld, (int)g_dtype, n.gate_bias, n.w, (int)n.w_dtype, y, (int)T, (int)H,
                                                  (int)std::max<i64>(n.groups, 1), (float)n.eps, (int)act, s.stream),
            "gated_norm_add");
         regs.pending = nullptr;
@@ -600,7 +610,8 @@ void Run::gated_mlp(const GatedMlpParams& L, const void* x, void* out) {
     // gate and up stay 32-bit until act(g) * u is formed; the way back takes its bias before it is rounded
     void* gu = linear(x, L.gate_up, T, H, EXEC_F32);
     void* h = arena.take(T * L.ff * elt(act));
-    LAUNCH(fn<GatedActFn>(FN_GATED_ACT)(h, gu, L.bg, L.bu, (int)L.b_dtype, (int)T, (int)L.ff, (int)L.act, (int)act, (int)EXEC_F32, s.stream),
+    if (L.extra) gate_at = static_cast<const float*>(gu) + 2 * L.ff, gate_ld = L.gate_up.N, gate_dtype = EXEC_F32;
+    LAUNCH(fn<GatedActFn>(FN_GATED_ACT)(h, gu, L.gate_up.N, L.bg, L.bu, (int)L.b_dtype, (int)T, (int)L.ff, (int)L.act, (int)act, (int)EXEC_F32, s.stream),
            "gated_act");
     if (L.bd && may_leave_bias) {
         product(out, h, L.down, T, L.ff, act);
@@ -620,7 +631,8 @@ void Run::mingru(const MinGruParams& L, const ExecItem& it, const void* x, void*
     // rounding of z would be carried along by the state)
     void* proj = linear(x, L.in_proj, T, H, EXEC_F32);
     void* y = arena.take(T * W * elt(act));
-    LAUNCH(fn<MinGruScanFn>(FN_MINGRU_SCAN)(y, proj, 3 * W, (int)EXEC_F32, L.bz, L.bx, (int)L.b_dtype, it.state, it.slot_stride, s.slot_ids,
+    if (L.extra) gate_at = static_cast<const float*>(proj) + 3 * W, gate_ld = L.in_proj.N, gate_dtype = EXEC_F32;
+    LAUNCH(fn<MinGruScanFn>(FN_MINGRU_SCAN)(y, proj, L.in_proj.N, (int)EXEC_F32, L.bz, L.bx, (int)L.b_dtype, it.state, it.slot_stride, s.slot_ids,
                                         s.cu_seqlens, (int)T, (int)s.B, (int)W, (int)it.n_slots, (int)s.max_q_len, (int)act, s.err, s.stream),
            "mingru_scan");
     product(out, y, L.out_proj, T, W, act);
@@ -629,6 +641,7 @@ void Run::mingru(const MinGruParams& L, const ExecItem& it, const void* x, void*
 void Run::latent_attention(const LatentAttentionParams& L, const ExecItem& it, const void* x, void* out) {
     const i64 T = s.T, H = p.H, nh = L.heads, kw = L.rank + L.rot_dim, e = elt(act);
     void* proj = linear(x, L.in_proj, T, H, act);
+    if (L.extra) gate_at = static_cast<const char*>(proj) + (L.in_proj.N - L.extra) * e, gate_ld = L.in_proj.N, gate_dtype = act;
     void* q_plain = arena.take(T * nh * L.dim * e);
     void* q_full = arena.take(T * nh * kw * e);
     LAUNCH(fn<LatentPrepFn>(FN_LATENT_PREP)(q_plain, q_full, proj, L.in_proj.N, (int)act, L.c_norm_w, (int)L.c_norm_dtype, (float)L.eps,

@@ -88,9 +88,12 @@ struct LinearParams { ExecLinear w; i64 lda, out_dtype; };             // out [T
 struct ReadStreamParams { i64 reserved; };
 // x += group_rms_norm(pending * sigmoid(y . gate^T + gate_bias)) * w, then y = x: a sublayer's result joins the stream.
 // gate.w null: no gate. y is the sublayer's input when the record starts.
-struct GatedNormAddParams { ExecLinear gate; const void* gate_bias; const void* w; i64 w_dtype, groups; double eps; };
+// stacked: the gate's rows lie behind the rows of the sublayer's own first product (its `extra`), which has formed the gate already.
+struct GatedNormAddParams { ExecLinear gate; const void* gate_bias; const void* w; i64 w_dtype, groups; double eps; i64 stacked; };
 // minGRU: in_proj stacks the rows of z, candidate and output gate ([3 * width, H]); the state is the item's slot [width].
-struct MinGruParams { ExecLinear in_proj, out_proj; const void* bz; const void* bx; i64 b_dtype, width; };
+// `extra` (here and below): rows stacked behind the part's own in its first matrix, whose products the part leaves for the
+// record after it (a gate over the same input).
+struct MinGruParams { ExecLinear in_proj, out_proj; const void* bz; const void* bx; i64 b_dtype, width, extra; };
 // Latent attention: in_proj stacks the queries' rows (heads * (dim + rot_dim)), the latent's (rank) and the shared
 // rotated key part's (rot_dim). absorb_k: [heads, rank, dim] (a head's key matrix transposed), expand_v: [heads, vdim,
 // rank]. The item's pages hold rows of rank + rot_dim values.
@@ -100,9 +103,10 @@ struct LatentAttentionParams {
     i64 heads, dim, rot_dim, vdim, rank; double scale;
     const void* c_norm_w; i64 c_norm_dtype; double eps;
     i64 rot; const void* inv_freq;
+    i64 extra;
 };
 // down . (act(gate . y + bg) * (up . y + bu)) + bd; act 0 silu, 1 gelu (tanh form); the biases may be null.
-struct GatedMlpParams { ExecLinear gate_up, down; const void* bg; const void* bu; const void* bd; i64 b_dtype, ff, act; };
+struct GatedMlpParams { ExecLinear gate_up, down; const void* bg; const void* bu; const void* bd; i64 b_dtype, ff, act, extra; };
 
 struct ExecOps { i64 n; const ExecOp* ops; };
 

@@ -26,12 +26,12 @@ _SIGNATURES = {
         "cellm_short_conv": [P, P, P, P, I, P, L, P, P, P, I, I, I, I, I, I, I, P, P],
         "cellm_qk_norm_rope": [P, P, L, P, P, I, F, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, I, P, P],
         "cellm_attention_plain": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P],
-        "cellm_gated_norm_add": [P, P, P, P, P, P, I, P, I, I, I, F, I, P],
+        "cellm_gated_norm_add": [P, P, P, P, L, I, P, P, I, P, I, I, I, F, I, P],
         "cellm_stream_cast": [P, P, L, I, P],
         "cellm_mingru_scan": [P, P, L, I, P, P, I, P, L, P, P, I, I, I, I, I, I, P, P],
         "cellm_latent_prep": [P, P, P, L, I, P, I, F, P, P, P, I, P, I, I, I, I, I, I, I, I, P, I, P, P],
         "cellm_head_product": [P, L, L, P, L, L, P, I, I, I, I, I, P],
-        "cellm_gated_act": [P, P, P, P, I, I, I, I, I, I, P],
+        "cellm_gated_act": [P, P, L, P, P, I, I, I, I, I, I, P],
         "cellm_bias_add": [P, P, P, I, I, I, I, P],
         "cellm_argmax": [P, P, I, I, P, P],
         "cellm_take_pending_tokens": [P, P, P, P, I, I, P, P],

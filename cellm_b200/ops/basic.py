@@ -210,15 +210,17 @@ def gated_norm_add(x: torch.Tensor, m: torch.Tensor, gate: Optional[torch.Tensor
                    w: torch.Tensor, groups: int, eps: float, want_copy: bool = True,
                    m_bias: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """x [T, H] float32 += group_rms_norm((m + m_bias) * sigmoid(gate + gate_bias)) * w, in place (gate None: no gate;
-    m_bias None: none). m and gate are of the activations' type, the biases of w's. Returns the new stream in that type (x itself for float32), or None if not wanted."""
-    require_cuda(x, m, gate, gate_bias, w, m_bias)
+    m_bias None: none). m is of the activations' type, gate too or float32 (it may be a view of columns of a wider matrix), the biases of w's. Returns the new stream in that type (x itself for float32), or None if not wanted."""
+    require_cuda(x, m, gate_bias, w, m_bias)
     T, H = x.shape
-    if x.dtype != torch.float32 or m.shape != x.shape or (gate is not None and (gate.shape != x.shape or gate.dtype != m.dtype)):
-        raise ValueError("gated_norm_add: x float32 [T, H]; m and gate [T, H] of one element type")
+    if x.dtype != torch.float32 or m.shape != x.shape or (gate is not None and (gate.shape != x.shape or gate.stride(1) != 1 or
+                                                                              gate.dtype not in (m.dtype, torch.float32))):
+        raise ValueError("gated_norm_add: x float32 [T, H]; m [T, H]; gate [T, H] of m's element type or float32, rows dense")
     if w.numel() != H or any(b is not None and (b.numel() != H or b.dtype != w.dtype) for b in (gate_bias, m_bias)):
         raise ValueError("gated_norm_add: w and gate_bias have H values of one element type")
     y = torch.empty_like(m) if (want_copy and m.dtype != torch.float32) else None
-    check(fn(_LIB, "cellm_gated_norm_add")(ptr(x), ptr(m), ptr(m_bias), ptr(gate), ptr(gate_bias), ptr(w), tag(w), ptr(y), T, H, int(groups),
+    check(fn(_LIB, "cellm_gated_norm_add")(ptr(x), ptr(m), ptr(m_bias), ptr(gate), gate.stride(0) if gate is not None else H,
+                                           tag(gate) if gate is not None else tag(m), ptr(gate_bias), ptr(w), tag(w), ptr(y), T, H, int(groups),
                                            float(eps), tag(m), stream_of(x)), "gated_norm_add")
     return y if y is not None else (x if want_copy else None)
 
@@ -263,7 +265,7 @@ def gated_act(gu: torch.Tensor, bg: Optional[torch.Tensor], bu: Optional[torch.T
     T, two_ff = gu.shape
     h = torch.empty((T, two_ff // 2), dtype=out_dtype, device=gu.device)
     wt = tag(bg) if bg is not None else tag(out_dtype)
-    check(fn(_LIB, "cellm_gated_act")(ptr(h), ptr(gu), ptr(bg), ptr(bu), wt, T, two_ff // 2, {"silu": 0, "gelu_tanh": 1}[act],
+    check(fn(_LIB, "cellm_gated_act")(ptr(h), ptr(gu), gu.stride(0), ptr(bg), ptr(bu), wt, T, two_ff // 2, {"silu": 0, "gelu_tanh": 1}[act],
                                       tag(h), tag(gu), stream_of(gu)), "gated_act")
     return h
 

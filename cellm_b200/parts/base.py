@@ -180,6 +180,12 @@ class Position(Part):
 
 
 class Mixer(Part):
+    def stack_behind_input(self, weight: torch.Tensor) -> bool:
+        """Offers the part rows [n, hidden] to stack behind its own first matrix, so that one product over the part's
+        input forms them too (a gate over the same input, for instance). A part that takes them leaves their products
+        for the record after it and returns True; the default declines."""
+        return False
+
     @classmethod
     def cache_need(cls, params: dict):
         """PagedKV, FixedState or None."""
@@ -195,6 +201,10 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    def stack_behind_input(self, weight: torch.Tensor) -> bool:
+        """As Mixer.stack_behind_input."""
+        return False
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 

@@ -62,11 +62,17 @@ class GatedPostNormBlock(Block):
         for n in (mixer_norm, feed_forward_norm):
             if n is not None and not all(hasattr(n, a) for a in ("weight", "eps", "groups")):
                 raise ConfigError("gated_post_norm: the norms must be RMS norms (weight, eps, groups)")
-        self.gates = {}
+        self.gates, self.stacked = {}, {}
         if params.get("gate"):
             for name in ("mixer", "feed_forward"):
                 if name + "_gate" in weights:
                     self.gates[name] = (Linear(weights[name + "_gate"], dtype), weights[name + "_gate_bias"].contiguous())
+                    # a sublayer that can form the gate with its own first product (both read the sublayer's input) is
+                    # given the gate's rows; the gate-and-norm record then finds the gate where that product left it
+                    part = getattr(self, name)
+                    self.stacked[name] = bool(params.get("stack_gates", True)) and part.stack_behind_input(weights[name + "_gate"])
+                    if self.stacked[name]:          # no second copy: the block's own matrix is those rows of the part's
+                        self.gates[name] = (Linear(part.stacked_rows(), dtype), self.gates[name][1])
         self._keep = []
 
     def _join(self, emitter, name: str, norm) -> None:
@@ -81,6 +87,7 @@ class GatedPostNormBlock(Block):
             bias = bias.to(norm.weight.dtype).contiguous()      # the kernel reads bias and norm weight as one element type
             self._keep.append(bias)
             p.gate, p.gate_bias = R.linear(lin.weight), bias.data_ptr()
+            p.stacked = int(self.stacked.get(name, False))
         p.w, p.w_dtype, p.groups, p.eps = norm.weight.data_ptr(), tag(norm.weight), norm.groups, norm.eps
         emitter.native(R.GATED_NORM_ADD, p, part=self)
 

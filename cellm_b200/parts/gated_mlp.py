@@ -39,7 +39,18 @@ class GatedMLP(FeedForward):
             self.bg = weights["gate_bias"].contiguous()
             self.bu = weights["up_bias"].to(self.bg.dtype).contiguous()
             self.bd = weights["down_bias"].to(self.bg.dtype).contiguous()
+        self.extra = 0
         self._record = None
+
+    def stack_behind_input(self, weight: torch.Tensor) -> bool:
+        if self._record is not None or self.extra or weight.dtype != self.gate_up.weight.dtype or weight.shape[1] != self.H:
+            return False
+        self.gate_up = Linear(stack_rows(self.gate_up.weight, weight), self.dtype)
+        self.extra = int(weight.shape[0])
+        return True
+
+    def stacked_rows(self) -> torch.Tensor:
+        return self.gate_up.weight[self.gate_up.weight.shape[0] - self.extra:]
 
     def record(self):
         from ..ops._lib import tag
@@ -47,7 +58,7 @@ class GatedMLP(FeedForward):
         if self._record is None and self.gate_up.weight.dtype == self.dtype == self.down.weight.dtype:
             p = R.GatedMlpParams(R.linear(self.gate_up.weight), R.linear(self.down.weight), R.ptr(self.bg), R.ptr(self.bu),
                                  R.ptr(self.bd), tag(self.bg) if self.bg is not None else tag(self.dtype), self.ff,
-                                 ACTIVATIONS[self.activation])
+                                 ACTIVATIONS[self.activation], self.extra)
             self._record = R.Record(R.GATED_MLP, p, part=self)
         return self._record
 
@@ -63,7 +74,7 @@ class GatedMLP(FeedForward):
         rec = self.record()
         if rec is not None:
             return part_program(self.dtype, x.device, self.H).run_part(rec, x, ctx)
-        gu = self.gate_up(x, out_dtype=torch.float32)
+        gu = self.gate_up(x, out_dtype=torch.float32)[:, :2 * self.ff]
         y = self.down(ops.gated_act(gu, self.bg, self.bu, self.activation, self.dtype), out_dtype=torch.float32)
         if self.bd is not None:
             y = y + self.bd.to(torch.float32)

@@ -57,7 +57,18 @@ class LatentAttentionMixer(Mixer):
             raise ConfigError("latent_attention: the position encoding must be a rotation of interleaved pairs "
                               "over at most rot_dim values")
         self.rot, self.inv_freq = int(rot[0]), rot[2]
+        self.extra = 0
         self._record = None
+
+    def stack_behind_input(self, weight: torch.Tensor) -> bool:
+        if self._record is not None or self.extra or weight.dtype != self.in_proj.weight.dtype or weight.shape[1] != self.H:
+            return False
+        self.in_proj = Linear(stack_rows(self.in_proj.weight, weight), self.dtype)
+        self.extra = int(weight.shape[0])
+        return True
+
+    def stacked_rows(self) -> torch.Tensor:
+        return self.in_proj.weight[self.in_proj.weight.shape[0] - self.extra:]
 
     def record(self):
         from ..ops._lib import tag
@@ -69,7 +80,7 @@ class LatentAttentionMixer(Mixer):
             p.absorb_k, p.expand_v = self.absorb_k.data_ptr(), self.expand_v.data_ptr()
             p.heads, p.dim, p.rot_dim, p.vdim, p.rank, p.scale = self.nh, self.d, self.r, self.vd, self.rank, self.scale
             p.c_norm_w, p.c_norm_dtype, p.eps = self.c_norm_w.data_ptr(), tag(self.c_norm_w), self.eps
-            p.rot, p.inv_freq = self.rot, R.ptr(self.inv_freq)
+            p.rot, p.inv_freq, p.extra = self.rot, R.ptr(self.inv_freq), self.extra
             self._record = R.Record(R.LATENT_ATTENTION, p, keep=[self.inv_freq], part=self)
         return self._record
 

@@ -43,14 +43,25 @@ class MinGRUMixer(Mixer):
         if params.get("bias", True):
             self.bz = weights["z_bias"].contiguous()
             self.bx = weights["x_bias"].to(self.bz.dtype).contiguous()
+        self.extra = 0
         self._record = None
+
+    def stack_behind_input(self, weight: torch.Tensor) -> bool:
+        if self._record is not None or self.extra or weight.dtype != self.in_proj.weight.dtype or weight.shape[1] != self.H:
+            return False
+        self.in_proj = Linear(stack_rows(self.in_proj.weight, weight), self.dtype)
+        self.extra = int(weight.shape[0])
+        return True
+
+    def stacked_rows(self) -> torch.Tensor:
+        return self.in_proj.weight[self.in_proj.weight.shape[0] - self.extra:]
 
     def record(self):
         from ..ops._lib import tag
         from ..runtime import records as R
         if self._record is None and self.in_proj.weight.dtype == self.dtype == self.out_proj.weight.dtype:
             p = R.MinGruParams(R.linear(self.in_proj.weight), R.linear(self.out_proj.weight), R.ptr(self.bz), R.ptr(self.bx),
-                               tag(self.bz) if self.bz is not None else tag(self.dtype), self.W)
+                               tag(self.bz) if self.bz is not None else tag(self.dtype), self.W, self.extra)
             self._record = R.Record(R.MINGRU, p, part=self)
         return self._record
 
@@ -66,7 +77,7 @@ class MinGRUMixer(Mixer):
         rec = self.record()
         if rec is not None:
             return part_program(self.dtype, x.device, self.H).run_part(rec, x, ctx, cache)
-        proj = self.in_proj(x, out_dtype=torch.float32)
+        proj = self.in_proj(x, out_dtype=torch.float32)[:, :3 * self.W]
         y = ops.mingru_scan(proj, self.bz, self.bx, cache.state, ctx.slot_ids, ctx.cu_seqlens, self.dtype, ctx.err, ctx.max_q_len)
         return self.out_proj(y)
 

@@ -71,22 +71,22 @@ class ReadStreamParams(Structure):
 
 
 class GatedNormAddParams(Structure):
-    _fields_ = [("gate", ExecLinear), ("gate_bias", PTR), ("w", PTR), ("w_dtype", I64), ("groups", I64), ("eps", F64)]
+    _fields_ = [("gate", ExecLinear), ("gate_bias", PTR), ("w", PTR), ("w_dtype", I64), ("groups", I64), ("eps", F64), ("stacked", I64)]
 
 
 class MinGruParams(Structure):
-    _fields_ = [("in_proj", ExecLinear), ("out_proj", ExecLinear), ("bz", PTR), ("bx", PTR), ("b_dtype", I64), ("width", I64)]
+    _fields_ = [("in_proj", ExecLinear), ("out_proj", ExecLinear), ("bz", PTR), ("bx", PTR), ("b_dtype", I64), ("width", I64), ("extra", I64)]
 
 
 class LatentAttentionParams(Structure):
     _fields_ = [("in_proj", ExecLinear), ("out_proj", ExecLinear), ("absorb_k", PTR), ("expand_v", PTR),
                 ("heads", I64), ("dim", I64), ("rot_dim", I64), ("vdim", I64), ("rank", I64), ("scale", F64),
-                ("c_norm_w", PTR), ("c_norm_dtype", I64), ("eps", F64), ("rot", I64), ("inv_freq", PTR)]
+                ("c_norm_w", PTR), ("c_norm_dtype", I64), ("eps", F64), ("rot", I64), ("inv_freq", PTR), ("extra", I64)]
 
 
 class GatedMlpParams(Structure):
     _fields_ = [("gate_up", ExecLinear), ("down", ExecLinear), ("bg", PTR), ("bu", PTR), ("bd", PTR), ("b_dtype", I64),
-                ("ff", I64), ("act", I64)]
+                ("ff", I64), ("act", I64), ("extra", I64)]
 
 
 class ExecOps(Structure):

@@ -91,20 +91,23 @@ def test_decode_step_kernels(monkeypatch):
     run_step(model, plan, [1, 1, 1], [40, 7, 300])
     assert names_of(rec) == [
         "embed", "stream_cast",
-        "gemm_tcgen05", "mingru_scan", "gemm_tcgen05",                          # z | candidate | gate, the recurrence, the way out
-        "gemm_tcgen05", "gated_norm_add",                                        # the gate's product, gate + norm + sum
+        "gemm_tcgen05", "mingru_scan", "gemm_tcgen05",                          # z | candidate | gate | the stream's gate, the recurrence, the way out
+        "gated_norm_add",                                                        # gate + norm + sum (the gate lies behind the product's own columns)
         "gemm_tcgen05", "latent_prep", "head_product", "attention_latent", "head_product", "gemm_tcgen05",
-        "gemm_tcgen05", "gated_norm_add",
-        "gemm_tcgen05", "gated_act", "gemm_tcgen05",                             # gate | up, activation, the way back
-        "gemm_tcgen05", "gated_norm_add",                                        # (its bias is added by the gate-and-norm kernel)
+        "gated_norm_add",
+        "gemm_tcgen05", "gated_act", "gemm_tcgen05",                             # gate | up | the stream's gate, activation, the way back
+        "gated_norm_add",                                                        # (its bias is added by the gate-and-norm kernel)
         "add_rmsnorm", "gemm_tcgen05"]
     prep = rec.of("cellm_latent_prep")[0]
     assert prep[15:22] == (3, 4, 32, 16, 64, 16, prep[21]) and prep[12] is not None          # tokens, heads, dim, rot_dim, rank, rot; a cache to write
     att = rec.of("cellm_attention_latent")[0]
     assert (att[9], att[10], att[14], att[15], att[16]) == (3, 3, 4, 80, 64)                 # requests, tokens, heads, row width, value width
     norm = rec.of("cellm_gated_norm_add")[0]
-    assert (norm[8], norm[9], norm[10]) == (3, 128, 2) and norm[3] is not None and norm[7] is not None and norm[2] is None
+    assert (norm[10], norm[11], norm[12]) == (3, 128, 2) and norm[3] is not None and norm[9] is not None and norm[2] is None
+    assert (norm[4], norm[5]) == (3 * 192 + 128, 0)                                           # the gate: 32-bit, behind z, candidate and gate
+    assert rec.of("cellm_gated_norm_add")[1][4:6] == (4 * 48 + 80 + 128, 1)                   # behind queries, latent and key part
     assert rec.of("cellm_gated_norm_add")[2][2] is not None                                   # the feed-forward's last bias
+    assert [g[4] for g in rec.of("cellm_gemm_tcgen05")][:1] == [3 * 192 + 128]
     final = rec.of("cellm_add_rmsnorm")[0]
     assert final[8] == 2                                                                      # the model's norm is in groups too
     assert rec.of("cellm_embed")[0][7] == 3.0

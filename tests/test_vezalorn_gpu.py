@@ -163,8 +163,9 @@ def sharp_attention_model(folder, seed, scale):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_sharp_attention_reaches_far_keys(tmp_path, dtype):
     # bfloat16 rounds a score of size s by s / 256, which a peaked softmax turns into that share of its weights: the
-    # 16-bit run gets scores a third as large, still peaked enough that one lost key shows
-    folder = sharp_attention_model(tmp_path / "sharp", 5, 1.5 if dtype == "float32" else 0.5)
+    # 16-bit run gets smaller scores (up to 27 instead of 200), still so peaked that the heaviest key has two fifths of
+    # the weight in the median and one lost key shows
+    folder = sharp_attention_model(tmp_path / "sharp", 5, 1.5 if dtype == "float32" else 0.2)
     cfg, w = load_plain(folder)
     rng = np.random.default_rng(3)
     toks = rng.integers(0, cfg["vocab"], 700).tolist()
@@ -196,6 +197,17 @@ def test_sharp_attention_reaches_far_keys(tmp_path, dtype):
 
 
 # ------------------------------------------------------------------------------------------ generation
+def check_greedy_tokens(cfg, w, prompt, out, dtype):
+    """Teacher-forced on the engine's own tokens: each is the plain model's arg-max given the tokens before it, or lies
+    within the precision's bound of it."""
+    seq = list(prompt) + list(out[:-1])
+    ref = plain.forward(cfg, w, seq)[len(prompt) - 1:].numpy()
+    tol = 2 * K[dtype] * (1 + np.abs(ref).max())
+    for j, t in enumerate(out):
+        best = int(ref[j].argmax())
+        assert t == best or ref[j][best] - ref[j][t] <= tol, f"token {j}: {t} where the plain model has {best}"
+
+
 @pytest.mark.parametrize("name", ["a", "c"])
 def test_greedy_generation_through_the_engine(models, name):
     from cellm_b200 import Engine, SamplingParams
@@ -207,12 +219,7 @@ def test_greedy_generation_through_the_engine(models, name):
     outs = eng.generate(prompts, SamplingParams.greedy(12, stop_eos=False))
     for prompt, out in zip(prompts, outs):
         assert len(out) == 12
-        seq = list(prompt) + list(out[:-1])
-        ref = plain.forward(cfg, w, seq)[len(prompt) - 1:].numpy()
-        tol = 2 * K["float32"] * (1 + np.abs(ref).max())
-        for j, t in enumerate(out):
-            best = int(ref[j].argmax())
-            assert t == best or ref[j][best] - ref[j][t] <= tol, f"token {j}: {t} where the plain model has {best}"
+        check_greedy_tokens(cfg, w, prompt, out, "float32")
     s = eng.stats()
     assert s["idle"] and s["free_pages"] == s["total_pages"] and s["free_slots"] == 3
 
@@ -220,13 +227,19 @@ def test_greedy_generation_through_the_engine(models, name):
 def test_bfloat16_generation_runs_ahead_and_frees(models):
     from cellm_b200 import Engine, SamplingParams
     folder, reqs, _ = models["c"]
+    cfg, w = load_plain(folder)
     prompts = list(reqs.values())
     eng = Engine(folder, dtype="bfloat16", tokens_per_block=16, total_blocks=80, max_num_seqs=4, max_batch_tokens=64,
                  prefill_chunk=32)
     outs = eng.generate(prompts, SamplingParams.greedy(20, stop_eos=False))
     assert all(len(o) == 20 for o in outs)
+    for prompt, out in zip(prompts, outs):
+        check_greedy_tokens(cfg, w, prompt, out, "bfloat16")
+    # slots and pages given back and used again: the plain model's tokens again (in another batch the kernels that serve
+    # a step may differ, so a near-tie may fall the other way: each run is held to the plain model, not to the other)
     again = eng.generate(prompts[:2], SamplingParams.greedy(20, stop_eos=False))
-    assert again == outs[:2]                       # slots and pages given back and used again give the same tokens
+    for prompt, out in zip(prompts[:2], again):
+        check_greedy_tokens(cfg, w, prompt, out, "bfloat16")
     s = eng.stats()
     assert s["idle"] and s["free_pages"] == s["total_pages"]
 
@@ -255,6 +268,10 @@ def test_gated_norm_add(dtype, H, groups, gate):
     v = md * torch.sigmoid(zd + bd) if gate else md
     want = x.double() + plain.group_rms_norm(v, wd, groups, 1e-5)
     xd = x.to(DEV)
+    if gate and groups == 2:        # the gate as 32-bit columns of a wider matrix (where a sublayer's first product leaves it)
+        wide = torch.zeros(T, H + 24, device=DEV)
+        wide[:, 16:16 + H] = z.float()
+        z = wide[:, 16:16 + H]
     y = ops.gated_norm_add(xd, m, z if gate else None, b if gate else None, w, groups, 1e-5, m_bias=c)
     torch.testing.assert_close(xd.cpu().double(), want, rtol=1e-5, atol=1e-5)
     torch.testing.assert_close(y.cpu().double(), want.to(dtype).double(), rtol=1e-2 if dtype == torch.bfloat16 else 1e-5, atol=1e-5)
