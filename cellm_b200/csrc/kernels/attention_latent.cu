@@ -3,7 +3,8 @@
 // values are one tile in shared memory. Serves prompt portions and decoded tokens alike.
 //
 // A CTA takes 64 consecutive (token, head) rows of one request's portion (the queries lie [T, heads, kw], so these are
-// 64 consecutive rows of kw values) and walks the keys in blocks of BN through the block table (cp.async, two stages).
+// 64 consecutive rows of kw values) and walks the keys in blocks of BN through the block table (cp.async, two stages;
+// a block's keys are worked on in runs of SUB, which is what the score registers hold).
 // Its warps are 4 groups of 16 rows times NC groups of DVW value columns: a warp forms S = Q K^T for its 16 rows and
 // the block's keys (the NC warps of a row group each form the same S: the scores cost kw/dv of the values' work, and
 // nothing has to pass between warps), keeps the running maximum and sum of flash attention in registers, and adds
@@ -18,7 +19,7 @@ namespace {
 
 constexpr int LA_BM = 64;
 
-template <int DVW, int BN, int MAXT>
+template <int DVW, int BN, int SUB, int MAXT>
 __global__ void __launch_bounds__(MAXT)
 latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool,
@@ -99,11 +100,16 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
-        const __nv_bfloat16* ks_ = k_s + stage * BN * stride;
         if (r0 + rw * 16 < rows) {           // (a decoded token's heads fill one or two of the four row groups)
-        float s[BN / 8][4];
+        // the block's keys in runs of SUB: scores, softmax and values of one run after the other (a block is what is
+        // fetched and waited for at once; a run is what the score registers hold)
+#pragma unroll 1
+        for (int sub = 0; sub < BN / SUB; ++sub) {
+        if ((kb * BN + sub * SUB) >= key_end) break;
+        const __nv_bfloat16* ks_ = k_s + (stage * BN + sub * SUB) * stride;
+        float s[SUB / 8][4];
 #pragma unroll
-        for (int n = 0; n < BN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+        for (int n = 0; n < SUB / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
         const __nv_bfloat16* q_row = q_s + (rw * 16 + (lane & 15)) * stride + (lane >> 4) * 8;
         const __nv_bfloat16* k_row = ks_ + ((lane & 7) + ((lane >> 4) << 3)) * stride + ((lane >> 3) & 1) * 8;
 #pragma unroll 4
@@ -111,7 +117,7 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
             uint32_t qf[4];
             ldmatrix_x4(qf, q_row + k0);
 #pragma unroll
-            for (int n2 = 0; n2 < BN / 16; ++n2) {
+            for (int n2 = 0; n2 < SUB / 16; ++n2) {
                 uint32_t kf[4];
                 ldmatrix_x4(kf, k_row + n2 * 16 * stride + k0);
                 mma_bf16(s[2 * n2], qf, kf[0], kf[1]);
@@ -119,10 +125,10 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
             }
         }
         // mask (a key after the row's own position), running maximum and sum
-        const int j0 = kb * BN + (lane & 3) * 2;
+        const int j0 = kb * BN + sub * SUB + (lane & 3) * 2;
         float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
-        for (int n = 0; n < BN / 8; ++n) {
+        for (int n = 0; n < SUB / 8; ++n) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int j = j0 + n * 8 + e;
@@ -144,9 +150,9 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
         m_a = mn_a;
         m_b = mn_b;
         float sum_a = 0.f, sum_b = 0.f;
-        uint32_t pf[BN / 16][4];
+        uint32_t pf[SUB / 16][4];
 #pragma unroll
-        for (int n = 0; n < BN / 8; ++n) {
+        for (int n = 0; n < SUB / 8; ++n) {
             const float p0 = fast_exp2(fmaf(s[n][0], scale_log2e, -use_a)), p1 = fast_exp2(fmaf(s[n][1], scale_log2e, -use_a));
             const float p2 = fast_exp2(fmaf(s[n][2], scale_log2e, -use_b)), p3 = fast_exp2(fmaf(s[n][3], scale_log2e, -use_b));
             sum_a += p0 + p1;
@@ -161,7 +167,7 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
         // O += P V over this warp's DVW columns of the rows' first dv values
         const __nv_bfloat16* v_row = ks_ + ((lane & 7) + (((lane >> 3) & 1) << 3)) * stride + cg * DVW + (lane >> 4) * 8;
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
+        for (int kk = 0; kk < SUB / 16; ++kk) {
 #pragma unroll
             for (int n2 = 0; n2 < NT / 2; ++n2) {
                 uint32_t vf[4];
@@ -169,6 +175,7 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                 mma_bf16(o[2 * n2], pf[kk], vf[0], vf[1]);
                 mma_bf16(o[2 * n2 + 1], pf[kk], vf[2], vf[3]);
             }
+        }
         }
         }
         __syncthreads();
@@ -250,7 +257,11 @@ int value_columns(int dv) {
     if (dv % 16 == 0 && dv / 16 <= 8) return 16;
     return 0;
 }
-int keys_per_block(int dvw) { return dvw == 64 ? 64 : 32; }
+// keys fetched and waited for at once (256 value columns a warp: 64 where two such stages fit beside the queries)
+int keys_per_block(int dvw, int kw) {
+    if (dvw == 256) return (size_t)(LA_BM + 128) * (kw + 8) * 2 + 2048 <= 227 * 1024 ? 64 : 32;
+    return dvw == 64 ? 64 : 32;
+}
 
 // Per-head products on the tensor cores: out[t, h, n] = sum_k in[t, h, k] * w[h][n][k]. A CTA forms 64 tokens by 64
 // outputs of one head: both operands' tiles wait whole in shared memory (K at most 512), each of the four warps forms
@@ -317,7 +328,7 @@ CELLM_API int cellm_attention_latent_supports(int kw, int dv) {
     if (kw <= 0 || dv <= 0 || dv > kw || (kw & 15) || (dv & 15)) return 0;
     const int dvw = value_columns(dv);
     if (!dvw) return 0;
-    const size_t smem = (size_t)(LA_BM + 2 * keys_per_block(dvw)) * (kw + 8) * 2;
+    const size_t smem = (size_t)(LA_BM + 2 * keys_per_block(dvw, kw)) * (kw + 8) * 2 + 2048;
     return smem <= 227 * 1024 ? 1 : 0;
 }
 
@@ -332,24 +343,25 @@ CELLM_API int cellm_attention_latent(void* out, float* part_o, float* part_ml, c
     if (!cellm_attention_latent_supports(kw, dv) || nh <= 0 || page_size <= 0 || nsplit < 1 || !(scale > 0.f)) return CELLM_ERR_SIZE;
     if (((uintptr_t)q & 15) || ((uintptr_t)pool & 15) || ((uintptr_t)out & 3)) return CELLM_ERR_ALIGN;
     if (nsplit > 1 && (!part_o || !part_ml)) return CELLM_ERR_ARG;
-    const int dvw = value_columns(dv), bn = keys_per_block(dvw);
+    const int dvw = value_columns(dv), bn = keys_per_block(dvw, kw);
     const int threads = 128 * (dv / dvw);
     const size_t smem = (size_t)(LA_BM + 2 * bn) * (kw + 8) * 2;
     const float scale_log2e = scale * 1.4426950408889634f;
     const dim3 grid((unsigned)n_tiles, (unsigned)nsplit);
-#define LAUNCH(DVW, BN, MAXT)                                                                                            \
+#define LAUNCH(DVW, BN, SUB, MAXT)                                                                                       \
     do {                                                                                                                 \
         if (smem > 48 * 1024)                                                                                            \
-            cudaFuncSetAttribute(latent_flash_kernel<DVW, BN, MAXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        CELLM_RUN((latent_flash_kernel<DVW, BN, MAXT>), grid, threads, smem, stream, (__nv_bfloat16*)out, part_o, part_ml,  \
+            cudaFuncSetAttribute(latent_flash_kernel<DVW, BN, SUB, MAXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        CELLM_RUN((latent_flash_kernel<DVW, BN, SUB, MAXT>), grid, threads, smem, stream, (__nv_bfloat16*)out, part_o, part_ml,  \
                   (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, cu_seqlens, ctx_lens, block_table, bt_stride, B, T,  \
                   num_pages, page_size, nh, kw, dv, scale_log2e, nsplit, err);                                             \
     } while (0)
-    if (dvw == 256) LAUNCH(256, 32, 256);
-    else if (dvw == 128) LAUNCH(128, 32, 512);
-    else if (dvw == 64) LAUNCH(64, 64, 512);
-    else if (dvw == 32) LAUNCH(32, 32, 1024);
-    else LAUNCH(16, 32, 1024);
+    if (dvw == 256 && bn == 64) LAUNCH(256, 64, 32, 256);
+    else if (dvw == 256) LAUNCH(256, 32, 32, 256);
+    else if (dvw == 128) LAUNCH(128, 32, 32, 512);
+    else if (dvw == 64) LAUNCH(64, 64, 64, 512);
+    else if (dvw == 32) LAUNCH(32, 32, 32, 1024);
+    else LAUNCH(16, 32, 32, 1024);
 #undef LAUNCH
     if (nsplit > 1)
         CELLM_RUN(latent_merge_kernel, (unsigned)((size_t)T * nh), dv >= 256 ? 256 : (dv >= 128 ? 128 : 64), (size_t)nsplit * 2 * sizeof(float), stream, (__nv_bfloat16*)out, part_o,

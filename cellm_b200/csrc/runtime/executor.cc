@@ -661,8 +661,8 @@ void Run::latent_attention(const LatentAttentionParams& L, const ExecItem& it, c
     else if (L.rank % 64 == 0 && L.rank / 64 <= 4) dvw = 64;
     else if (L.rank % 32 == 0 && L.rank / 32 <= 8) dvw = 32;
     else if (L.rank % 16 == 0 && L.rank / 16 <= 8) dvw = 16;
-    const i64 bn = dvw == 64 ? 64 : 32;
-    if (p.latent_tc && act == EXEC_BF16 && L.scale > 0 && dvw && kw % 16 == 0 && (64 + 2 * bn) * (kw + 8) * 2 <= 227 * 1024) {
+    const i64 bn = dvw == 256 ? ((64 + 128) * (kw + 8) * 2 + 2048 <= 227 * 1024 ? 64 : 32) : (dvw == 64 ? 64 : 32);
+    if (p.latent_tc && act == EXEC_BF16 && L.scale > 0 && dvw && kw % 16 == 0 && (64 + 2 * bn) * (kw + 8) * 2 + 2048 <= 227 * 1024) {
         i64 n_tiles = 0;
         for (i64 b = 0; b < s.B; ++b) n_tiles += ceil_div(s.q_lens[b] * nh, 64);
         const i64 blocks = ceil_div(s.max_total_len, bn);
