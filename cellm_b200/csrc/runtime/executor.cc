@@ -669,7 +669,8 @@ void Run::latent_attention(const LatentAttentionParams& L, const ExecItem& it, c
         // pieces of the keys: what fills the SMs once (two CTAs an SM where two tiles of this width fit its shared
         // memory), of at least two blocks of keys each
         const i64 per_sm = std::min<i64>(2, std::max<i64>(1, 227 * 1024 / ((64 + 2 * bn) * (kw + 8) * 2)));
-        const i64 nsplit = std::max<i64>(1, std::min(ceil_div(per_sm * p.sms, n_tiles), blocks / 2));
+        // (rounded down: one CTA more than the SMs hold at once would wait for a second round by itself)
+        const i64 nsplit = std::max<i64>(1, std::min(per_sm * p.sms / n_tiles, blocks / 2));
         void *part_o = nullptr, *part_ml = nullptr;
         if (nsplit > 1) {
             const i64 rows = T * nh;

@@ -47,7 +47,7 @@ CONFIG_A = model_config(300, 96, 6.0, 1e-5, 4, [
 CONFIG_B = model_config(211, 72, 1.0, 1e-6, 1, [
     gru(40),
     attention(1, 24, 12, 20, 28, base=1000.0, mlp=dense(100)),
-    attention(5, 8, 4, 12, 36, base=250000.0, mlp=dense(64)),
+    attention(5, 8, 4, 12, 36, base=300000.0, mlp=dense(64)),
     gru(72, mlp=dense(90)),
 ])
 # sizes at which the tensor-core kernels serve the bfloat16 path (multiples of 16 everywhere)
