@@ -57,9 +57,16 @@ CONFIG_C = model_config(512, 128, 3.0, 1e-5, 2, [
     gru(128, mlp=dense(128)),
     attention(8, 16, 32, 16, 96, base=10000.0),
 ])
-CONFIGS = {"a": CONFIG_A, "b": CONFIG_B, "c": CONFIG_C}
-LENGTHS = {"a": [1, 9, 40, 64, 131, 77, 2], "b": [3, 55, 150, 18, 97], "c": [200, 1, 65, 129, 30, 260]}
-PAGE = {"a": 8, "b": 16, "c": 16}
+# sizes that are multiples of nothing: no 16-byte row anywhere, so every kernel's plain form serves both element types
+CONFIG_D = model_config(101, 54, 2.5, 1e-5, 3, [
+    attention(2, 10, 6, 14, 22, base=5000.0, mlp=dense(50)),
+    gru(30),
+    attention(7, 6, 2, 5, 9, base=20000.0),
+    gru(54, mlp=dense(33)),
+])
+CONFIGS = {"a": CONFIG_A, "b": CONFIG_B, "c": CONFIG_C, "d": CONFIG_D}
+LENGTHS = {"a": [1, 9, 40, 64, 131, 77, 2], "b": [3, 55, 150, 18, 97], "c": [200, 1, 65, 129, 30, 260], "d": [70, 2, 33, 140, 17]}
+PAGE = {"a": 8, "b": 16, "c": 16, "d": 4}
 
 
 def write_model(folder, config, seed, dtype="bfloat16", init=None):
@@ -402,7 +409,8 @@ def test_one_layer_alone(tmp_path, dtype, layer):
             check_close(traces.as_matrix(got[rid], len(toks)), plain.forward(cfg, w, toks).numpy(), dtype, f"{layer['type']} {fam} {rid}")
 
 
-@pytest.mark.parametrize("nh,kw,dv,page", [(8, 80, 64, 16), (16, 576, 512, 32), (5, 48, 32, 8), (3, 64, 48, 16), (2, 144, 128, 64)])
+@pytest.mark.parametrize("nh,kw,dv,page", [(8, 80, 64, 16), (16, 576, 512, 32), (5, 48, 32, 8), (3, 64, 48, 16), (2, 144, 128, 64),
+                                              (4, 400, 384, 16), (2, 112, 96, 8), (3, 96, 80, 16), (70, 32, 16, 16), (2, 800, 768, 16)])
 def test_latent_attention_kernel_against_plain_kernel_and_torch(nh, kw, dv, page):
     """The tensor-core kernel alone: portions of several requests at contexts that end inside a page and inside a block
     of keys, whole and cut into pieces, against 64-bit torch over the same rounded inputs and the plain kernel."""
