@@ -14,7 +14,7 @@
 #include "common.cuh"
 
 #define ATTN_PLAIN_THREADS 128
-#define ATTN_PLAIN_MAX_HD 1024
+#define ATTN_PLAIN_MAX_HD 2048
 
 template <typename TA>
 __global__ void __launch_bounds__(ATTN_PLAIN_THREADS)

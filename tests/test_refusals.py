@@ -78,7 +78,7 @@ def test_attention_kernels():
 
     def plain(nh=4, nkv=2, hd=64):
         return call("kernels_common", "cellm_attention_plain", A, A, A, A, A, A, A, 4, 8, 16, 2, nh, nkv, hd, hd, 0.125, 0, 1, A, None)
-    assert plain(hd=1032) == SIZE and plain(hd=0) == SIZE and plain(nh=5) == SIZE
+    assert plain(hd=2056) == SIZE and plain(hd=0) == SIZE and plain(nh=5) == SIZE
 
 
 def test_small_kernels():
