@@ -3,8 +3,8 @@ need, and (through the native runtime) the pages and the state slot each live
 request holds.
 
 Paged groups: keys and values of all order items with the same
-(kv heads, head size, window), pool [items, pages, kv heads, page size, head
-size] each for K and V (K alone for a group whose rows are keys and values at once); one page id of a group means that page in every item
+(kv heads, head size, window, value size), pool [items, pages, kv heads, page size, head
+size] each for K and V (V with rows of the value size where that differs) (K alone for a group whose rows are keys and values at once); one page id of a group means that page in every item
 of the group. The reference sizes one pool for all layers, convolution layers
 included (tools/infer/src/main.rs:386-392); here only items that keep keys
 have pages. State groups: [items, slots, *shape] for order items with
@@ -67,7 +67,8 @@ class CacheManager:
         for g, need in enumerate(self.paged_keys):
             shape = (members[("paged", g)], self.group_pages[g], need.num_kv_heads, self.page_size, need.head_dim)
             self.k_pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
-            self.v_pools.append(torch.zeros(shape, dtype=dtype, device=self.device) if need.values else None)
+            v_shape = shape[:4] + (need.value_dim or need.head_dim,)
+            self.v_pools.append(torch.zeros(v_shape, dtype=dtype, device=self.device) if need.values else None)
         for g, need in enumerate(self.state_keys):
             self.states.append(torch.zeros((members[("state", g)], self.num_slots) + tuple(need.shape),
                                            dtype=need.dtype, device=self.device))
@@ -167,4 +168,5 @@ class CacheManager:
     def bytes_per_token(self) -> int:
         """Bytes of keys and values one token occupies over all paged groups."""
         el = torch.empty((), dtype=self.dtype).element_size()
-        return sum((2 if v is not None else 1) * p.shape[0] * p.shape[2] * p.shape[4] * el for p, v in zip(self.k_pools, self.v_pools))
+        return sum(p.shape[0] * p.shape[2] * (p.shape[4] + (v.shape[4] if v is not None else 0)) * el
+                   for p, v in zip(self.k_pools, self.v_pools))

@@ -4,8 +4,9 @@ from .registry import (register_architecture, registered_architectures, resolve_
                        config_from_dict, load_config)
 from .lfm2 import Lfm2Config
 from .vezalorn import VezalornConfig
+from .tufadra import TufadraConfig
 from .engine_config import EngineConfig, parse_dtype
 
 __all__ = ["ConfigError", "PartSpec", "LayerSpec", "OrderEntry", "ModelPlan",
            "register_architecture", "registered_architectures", "resolve_architecture",
-           "config_from_dict", "load_config", "Lfm2Config", "VezalornConfig", "EngineConfig", "parse_dtype"]
+           "config_from_dict", "load_config", "Lfm2Config", "VezalornConfig", "TufadraConfig", "EngineConfig", "parse_dtype"]

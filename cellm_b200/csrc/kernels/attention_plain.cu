@@ -21,7 +21,7 @@ __global__ void __launch_bounds__(ATTN_PLAIN_THREADS)
 attention_plain_kernel(TA* __restrict__ out, const TA* __restrict__ q, const TA* __restrict__ k_pool,
                        const TA* __restrict__ v_pool, const int* __restrict__ positions,
                        const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
-                       int bt_stride, int num_pages, int page_size, int nh, int nkv, int hd, int hdv, float scale,
+                       int bt_stride, int num_pages, int page_size, int nh, int nkv, int hd, int hdv, int v_row, float scale,
                        int window, int* __restrict__ err) {
     constexpr int CH = ATTN_PLAIN_THREADS;
     extern __shared__ float smem[];
@@ -42,7 +42,7 @@ attention_plain_kernel(TA* __restrict__ out, const TA* __restrict__ q, const TA*
     float acc[ATTN_PLAIN_MAX_HD / CH];
 #pragma unroll
     for (int r = 0; r < ATTN_PLAIN_MAX_HD / CH; ++r) acc[r] = 0.f;
-    const size_t page_elems = (size_t)nkv * page_size * hd;
+    const size_t page_elems = (size_t)nkv * page_size * hd, v_page_elems = (size_t)nkv * page_size * v_row;
     for (int c0 = (lo / CH) * CH; c0 <= pos; c0 += CH) {
         __syncthreads();
         {   // page of key c0 + tid
@@ -88,7 +88,7 @@ attention_plain_kernel(TA* __restrict__ out, const TA* __restrict__ q, const TA*
                     const int pgj = pg[jj];
                     if (pgj < 0) continue;
                     const int j = c0 + jj;
-                    a += sc[jj] * to_float(v_pool[(size_t)pgj * page_elems + ((size_t)kvh * page_size + j % page_size) * hd + d]);
+                    a += sc[jj] * to_float(v_pool[(size_t)pgj * v_page_elems + ((size_t)kvh * page_size + j % page_size) * v_row + d]);
                 }
                 acc[r] = a;
             }
@@ -104,27 +104,47 @@ attention_plain_kernel(TA* __restrict__ out, const TA* __restrict__ q, const TA*
 
 // q: [T, nh*hd]; out: [T, nh*hdv]; pools: one layer's keys and values; positions[t] is the
 // token's place in its request (keys 0..positions[t] are read; the token's own
-// key must already be in the cache). A value is the first hdv entries of its row of hd
-// (hdv = hd for ordinary attention); v_pool may be k_pool itself, for a cache whose
-// rows serve as keys and, in their first part, as values.
-CELLM_API int cellm_attention_plain(void* out, const void* q, const void* k_pool, const void* v_pool,
-                                    const int* positions, const int* seq_of_token, const int* block_table,
-                                    int bt_stride, int num_pages, int page_size, int T, int nh, int nkv,
-                                    int hd, int hdv, float scale, int window, int dtype, int* err,
-                                    cudaStream_t stream) {
+// key must already be in the cache). Value rows are v_row wide and a value is a row's first hdv entries.
+static int attention_plain_impl(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                const int* positions, const int* seq_of_token, const int* block_table,
+                                int bt_stride, int num_pages, int page_size, int T, int nh, int nkv,
+                                int hd, int hdv, int v_row, float scale, int window, int dtype, int* err,
+                                cudaStream_t stream) {
     if (T <= 0) return CELLM_OK;
-    if (hd > ATTN_PLAIN_MAX_HD || hd <= 0 || hdv <= 0 || hdv > hd || nkv <= 0 || nh % nkv) return CELLM_ERR_SIZE;
+    if (hd > ATTN_PLAIN_MAX_HD || hd <= 0 || hdv <= 0 || hdv > v_row || hdv > ATTN_PLAIN_MAX_HD || nkv <= 0 || nh % nkv) return CELLM_ERR_SIZE;
     const size_t smem = (size_t)(hd + 2 * ATTN_PLAIN_THREADS) * sizeof(float);
     const unsigned grid = (unsigned)T * (unsigned)nh;
     if (dtype == CELLM_F32)
         CELLM_RUN(attention_plain_kernel<float>, grid, ATTN_PLAIN_THREADS, smem, stream,
             (float*)out, (const float*)q, (const float*)k_pool, (const float*)v_pool, positions, seq_of_token,
-            block_table, bt_stride, num_pages, page_size, nh, nkv, hd, hdv, scale, window, err);
+            block_table, bt_stride, num_pages, page_size, nh, nkv, hd, hdv, v_row, scale, window, err);
     else if (dtype == CELLM_BF16)
         CELLM_RUN(attention_plain_kernel<__nv_bfloat16>, grid, ATTN_PLAIN_THREADS, smem, stream,
             (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
             (const __nv_bfloat16*)v_pool, positions, seq_of_token, block_table, bt_stride, num_pages,
-            page_size, nh, nkv, hd, hdv, scale, window, err);
+            page_size, nh, nkv, hd, hdv, v_row, scale, window, err);
     else return CELLM_ERR_DTYPE;
     return CELLM_OK;
+}
+
+// Values in rows as wide as the keys' (hdv = hd for ordinary attention; hdv < hd with v_pool = k_pool for a cache
+// whose rows serve as keys and, in their first part, as values).
+CELLM_API int cellm_attention_plain(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                    const int* positions, const int* seq_of_token, const int* block_table,
+                                    int bt_stride, int num_pages, int page_size, int T, int nh, int nkv,
+                                    int hd, int hdv, float scale, int window, int dtype, int* err,
+                                    cudaStream_t stream) {
+    if (hdv > hd) return CELLM_ERR_SIZE;
+    return attention_plain_impl(out, q, k_pool, v_pool, positions, seq_of_token, block_table, bt_stride, num_pages, page_size, T, nh, nkv,
+                                hd, hdv, hd, scale, window, dtype, err, stream);
+}
+
+// Values of a width of their own: a pool of values [page][kv_head][slot][hdv] beside the keys' [..][hd].
+CELLM_API int cellm_attention_plain_wide(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                         const int* positions, const int* seq_of_token, const int* block_table,
+                                         int bt_stride, int num_pages, int page_size, int T, int nh, int nkv,
+                                         int hd, int hdv, float scale, int window, int dtype, int* err,
+                                         cudaStream_t stream) {
+    return attention_plain_impl(out, q, k_pool, v_pool, positions, seq_of_token, block_table, bt_stride, num_pages, page_size, T, nh, nkv,
+                                hd, hdv, hdv, scale, window, dtype, err, stream);
 }

@@ -1,0 +1,114 @@
+// Queries, keys and values on their way from the projection into the attention, in the general form: an RMS
+// norm of queries and keys taken per head or over the whole projection (all heads of a token at once), a
+// query temperature that grows with the position, keys and values of different widths, and the write of keys
+// and values into the request's pages. (The per-head norm with a rotation is qk_norm_rope.cu's.)
+//
+//   span 0: no norm;  span 1: every head by its own root mean square (weights [hd], the same for every head);
+//   span 2: all heads of a token by one root mean square (weights [heads * hd])
+//   q <- q * (1 + coef * ln(floor((pos + 1) / every) + 1))     (coef = 0: no temperature)
+//
+// Norm, temperature and positions are 32-bit. Rows of the projection: [nh * hd | nkv * hd | nkv * hdv].
+// Cache layout of one layer: keys [page][kv_head][slot in page][hd], values [page][kv_head][slot in page][hdv].
+#include "common.cuh"
+
+#define PREP_THREADS 256
+
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(PREP_THREADS)
+attn_prep_kernel(TA* __restrict__ q_out, const TA* __restrict__ qkv, long long row_stride, const TW* __restrict__ q_w,
+                 const TW* __restrict__ k_w, float eps, int span, float temp_coef, int temp_every,
+                 const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+                 int bt_stride, TA* __restrict__ k_pool, TA* __restrict__ v_pool, int num_pages, int page_size, int nh, int nkv,
+                 int hd, int hdv, int* __restrict__ err) {
+    extern __shared__ float smem[];          // [nh + nkv] a head's sum of squares, then its factor
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = PREP_THREADS / 32;
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    float temp = 1.f;
+    if (temp_coef != 0.f) temp = 1.f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.f);
+    long long page = -1;
+    if (nkv > 0) {
+        const int b = seq_of_token[t];
+        const int p = block_table[(size_t)b * bt_stride + pos / page_size];
+        if (p < 0 || p >= num_pages) {
+            if (threadIdx.x == 0) atomicOr(err, CELLM_DEV_BAD_PAGE);
+        } else {
+            page = p;
+        }
+    }
+    pdl_wait();
+    const TA* row = qkv + (size_t)t * row_stride;
+    const int heads = nh + nkv;
+    if (span != 0) {
+        for (int h = warp; h < heads; h += nwarps) {
+            const TA* src = row + (size_t)h * hd;
+            float ss = 0.f;
+            for (int i = lane; i < hd; i += 32) {
+                const float v = to_float(src[i]);
+                ss += v * v;
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) smem[h] = ss;
+        }
+        __syncthreads();
+        float fq = 0.f, fk = 0.f;
+        if (span == 2) {                     // every thread adds the heads' sums in the same order
+            for (int h = 0; h < nh; ++h) fq += smem[h];
+            for (int h = nh; h < heads; ++h) fk += smem[h];
+            fq = 1.0f / sqrtf(fq / (float)(nh * hd) + eps);
+            fk = nkv > 0 ? 1.0f / sqrtf(fk / (float)(nkv * hd) + eps) : 0.f;
+        }
+        __syncthreads();
+        for (int h = threadIdx.x; h < heads; h += PREP_THREADS)
+            smem[h] = span == 2 ? (h < nh ? fq : fk) : 1.0f / sqrtf(smem[h] / (float)hd + eps);
+        __syncthreads();
+    }
+    // queries
+    for (int i = threadIdx.x; i < nh * hd; i += PREP_THREADS) {
+        float v = to_float(row[i]);
+        if (span != 0) v = v * smem[i / hd] * to_float(q_w[span == 2 ? i : i % hd]);
+        q_out[(size_t)t * nh * hd + i] = from_float<TA>(v * temp);
+    }
+    if (page < 0) return;
+    const int slot = pos % page_size;
+    // keys
+    const TA* krow = row + (size_t)nh * hd;
+    for (int i = threadIdx.x; i < nkv * hd; i += PREP_THREADS) {
+        const int h = i / hd, c = i - h * hd;
+        float v = to_float(krow[i]);
+        if (span != 0) v = v * smem[nh + h] * to_float(k_w[span == 2 ? i : c]);
+        k_pool[((size_t)page * nkv + h) * page_size * hd + (size_t)slot * hd + c] = from_float<TA>(v);
+    }
+    // values
+    const TA* vrow = krow + (size_t)nkv * hd;
+    for (int i = threadIdx.x; i < nkv * hdv; i += PREP_THREADS) {
+        const int h = i / hdv, c = i - h * hdv;
+        v_pool[((size_t)page * nkv + h) * page_size * hdv + (size_t)slot * hdv + c] = vrow[i];
+    }
+}
+
+// qkv: [T, nh*hd + nkv*(hd + hdv)] (row pitch row_stride); q_out: [T, nh*hd]. nkv = 0: the rows hold queries only and
+// nothing is written. Weights: [hd] (span 1) or [nh*hd] and [nkv*hd] (span 2), null with span 0.
+CELLM_API int cellm_attn_prep(void* q_out, const void* qkv, long long row_stride, const void* q_w, const void* k_w, int w_dtype, float eps,
+                              int span, float temp_coef, int temp_every, const int* positions, const int* seq_of_token,
+                              const int* block_table, int bt_stride, void* k_pool, void* v_pool, int num_pages, int page_size, int T,
+                              int nh, int nkv, int hd, int hdv, int dtype, int* err, cudaStream_t stream) {
+    if (T <= 0) return CELLM_OK;
+    if (nh < 1 || nkv < 0 || hd < 1 || hdv < 1 || span < 0 || span > 2) return CELLM_ERR_SIZE;
+    if (span != 0 && (!q_w || (nkv > 0 && !k_w))) return CELLM_ERR_ARG;
+    if (temp_coef != 0.f && temp_every < 1) return CELLM_ERR_ARG;
+    if (nkv > 0 && (!block_table || !k_pool || !v_pool || page_size < 1)) return CELLM_ERR_ARG;
+    const size_t smem = (size_t)(nh + nkv) * sizeof(float);
+#define GO(TA, TW)                                                                                                           \
+    CELLM_RUN((attn_prep_kernel<TA, TW>), T, PREP_THREADS, smem, stream, (TA*)q_out, (const TA*)qkv, row_stride, (const TW*)q_w, \
+              (const TW*)k_w, eps, span, temp_coef, temp_every, positions, seq_of_token, block_table, bt_stride, (TA*)k_pool,  \
+              (TA*)v_pool, num_pages, page_size, nh, nkv, hd, hdv, err)
+    if (dtype == CELLM_F32 && (w_dtype == CELLM_F32 || span == 0)) GO(float, float);
+    else if (dtype == CELLM_F32 && w_dtype == CELLM_BF16) GO(float, __nv_bfloat16);
+    else if (dtype == CELLM_BF16 && w_dtype == CELLM_F32) GO(__nv_bfloat16, float);
+    else if (dtype == CELLM_BF16 && (w_dtype == CELLM_BF16 || span == 0)) GO(__nv_bfloat16, __nv_bfloat16);
+    else return CELLM_ERR_DTYPE;
+#undef GO
+    return CELLM_OK;
+}

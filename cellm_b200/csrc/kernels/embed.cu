@@ -5,6 +5,25 @@
 // in the device error word and its row is written as zeros.
 #include "common.cuh"
 
+// With a table of learned position vectors, out[t, :] += float(pos_table[positions[t], :]) (not scaled); a
+// position beyond the table sets the same error bit and adds nothing.
+template <typename T>
+__global__ void embed_pos_kernel(float* __restrict__ out, const T* __restrict__ table, const int* __restrict__ ids,
+                                 const T* __restrict__ pos_table, const int* __restrict__ positions, int max_pos, int H, int V,
+                                 float scale, int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int id = ids[t], pos = positions[t];
+    const bool ok = id >= 0 && id < V, pos_ok = pos >= 0 && pos < max_pos;
+    if ((!ok || !pos_ok) && threadIdx.x == 0) atomicOr(err, CELLM_DEV_BAD_TOKEN);
+    const T* row = table + (size_t)(ok ? id : 0) * H;
+    const T* prow = pos_table + (size_t)(pos_ok ? pos : 0) * H;
+    float* o = out + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        o[i] = (ok ? to_float(row[i]) * scale : 0.f) + (pos_ok ? to_float(prow[i]) : 0.f);
+}
+
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table,
                              const int* __restrict__ ids, int H, int V, float scale, int* __restrict__ err) {
@@ -37,6 +56,24 @@ CELLM_API int cellm_embed(float* out, const void* table, int table_dtype, const 
         CELLM_RUN_SERIAL(embed_kernel<float>, T, threads, 0, stream, out, (const float*)table, ids, H, V, scale, err);
     else if (table_dtype == CELLM_BF16)
         CELLM_RUN_SERIAL(embed_kernel<__nv_bfloat16>, T, threads, 0, stream, out, (const __nv_bfloat16*)table, ids, H, V, scale, err);
+    else
+        return CELLM_ERR_DTYPE;
+    return CELLM_OK;
+}
+
+// The same with learned position vectors added: pos_table [max_pos, H] of the table's element type.
+CELLM_API int cellm_embed_pos(float* out, const void* table, int table_dtype, const int* ids, const void* pos_table,
+                              const int* positions, int max_pos, int T, int H, int V, float scale, int* err,
+                              cudaStream_t stream) {
+    if (T <= 0) return CELLM_OK;
+    if (!pos_table || !positions || max_pos < 1) return CELLM_ERR_ARG;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == CELLM_F32)
+        CELLM_RUN_SERIAL(embed_pos_kernel<float>, T, threads, 0, stream, out, (const float*)table, ids, (const float*)pos_table,
+                         positions, max_pos, H, V, scale, err);
+    else if (table_dtype == CELLM_BF16)
+        CELLM_RUN_SERIAL(embed_pos_kernel<__nv_bfloat16>, T, threads, 0, stream, out, (const __nv_bfloat16*)table, ids,
+                         (const __nv_bfloat16*)pos_table, positions, max_pos, H, V, scale, err);
     else
         return CELLM_ERR_DTYPE;
     return CELLM_OK;

@@ -1,0 +1,305 @@
+// Routed feed-forward ("mixture of experts"): the router with its choice of experts, and the experts' two
+// products in the form that serves few tokens and the 32-bit path (a token's chosen experts are walked row by
+// row; every weight row a token needs is read once for it).
+//
+//   z = R h (32-bit sums);  s = sigmoid(z);  c = s + correction          (c chooses, s weighs)
+//   experts lie in `n_groups` equal runs of neighbours; a run's score is the sum of its two largest c (its
+//   only c for runs of one); only experts of the `keep` best runs can be chosen (the others count as -inf)
+//   the `top` experts with the largest c are chosen; their weights are s / (sum of the chosen s + 1e-20) * scale
+//   out = sum_k weight_k * D_k act(U_k h)  [+ sigmoid(g . h) * shared(h)]
+//
+// Ties go to the lower index. The chosen experts are listed by descending c, and every sum runs in an order
+// that depends on the sizes alone, so a token's result does not depend on what else is in the batch.
+#include "common.cuh"
+
+#define ROUTE_TPB 8
+#define ROUTE_THREADS 128
+
+__device__ __forceinline__ float cellm_activate(float z, int act) {
+    switch (act) {
+        case 0: return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));                    // gelu, exact
+        case 1: return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));   // gelu, tanh form
+        case 2: return z / (1.f + expf(-z));                                                 // silu
+        default: return fmaxf(z, 0.f);                                                       // relu
+    }
+}
+
+// A lane's share of the dot product of a weight row with a vector held as floats: pieces of 16 bytes where the
+// row allows it (`vec`), else element by element.
+template <typename TW>
+__device__ __forceinline__ float lane_dot(const TW* __restrict__ w, const float* __restrict__ v, int n, int lane, bool vec);
+template <>
+__device__ __forceinline__ float lane_dot<float>(const float* __restrict__ w, const float* __restrict__ v, int n, int lane, bool vec) {
+    float a = 0.f;
+    if (vec) {
+        for (int i = lane * 4; i < n; i += 128) {
+            const float4 x = *reinterpret_cast<const float4*>(w + i);
+            a += x.x * v[i] + x.y * v[i + 1] + x.z * v[i + 2] + x.w * v[i + 3];
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) a += w[i] * v[i];
+    }
+    return a;
+}
+template <>
+__device__ __forceinline__ float lane_dot<__nv_bfloat16>(const __nv_bfloat16* __restrict__ w, const float* __restrict__ v, int n, int lane,
+                                                        bool vec) {
+    float a = 0.f;
+    if (vec) {
+        for (int i = lane * 8; i < n; i += 256) {
+            const uint4 x = *reinterpret_cast<const uint4*>(w + i);
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(p[j]);
+                a += f.x * v[i + 2 * j] + f.y * v[i + 2 * j + 1];
+            }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) a += __bfloat162float(w[i]) * v[i];
+    }
+    return a;
+}
+template <typename TW> __device__ __forceinline__ bool rows_vectorise(const TW* base, long long ld, int n) {
+    constexpr int per = 16 / (int)sizeof(TW);
+    return (n % per) == 0 && (ld % per) == 0 && (((uintptr_t)base) & 15) == 0;
+}
+
+// ---- the router ----------------------------------------------------------------------------------------------------
+// One block takes ROUTE_TPB tokens: their inputs lie in shared memory, a warp forms one router row's sums for all of
+// them at once, then a warp a token chooses.
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_kernel(int* __restrict__ idx, float* __restrict__ wts, float* __restrict__ gate_out, const TA* __restrict__ y, long long ldy,
+             const TW* __restrict__ router, const TC* __restrict__ correction, int T, int H, int E, int top, int n_groups, int keep,
+             float scale, int has_gate) {
+    extern __shared__ float smem[];
+    float* hs = smem;                               // [TPB][H]
+    float* sc = hs + (size_t)ROUTE_TPB * H;         // [TPB][E + 1]: logits, then s
+    float* ch = sc + ROUTE_TPB * (E + 1);           // [TPB][E]: choice scores
+    float* gs = ch + ROUTE_TPB * E;                 // [TPB][n_groups]: scores of the runs
+    float* kf = gs + ROUTE_TPB * n_groups;          // [TPB][n_groups]: 1 = the run is kept
+    float* sel = kf + ROUTE_TPB * n_groups;         // [TPB][top]: s of the chosen, by rank
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = ROUTE_THREADS / 32;
+    const int t0 = blockIdx.x * ROUTE_TPB, nt = min(ROUTE_TPB, T - t0);
+    pdl_trigger();
+    pdl_wait();
+    for (int i = threadIdx.x; i < ROUTE_TPB * H; i += ROUTE_THREADS) {
+        const int j = i / H, c = i - j * H;
+        hs[i] = j < nt ? to_float(y[(size_t)(t0 + j) * ldy + c]) : 0.f;
+    }
+    __syncthreads();
+    const int rows = E + (has_gate ? 1 : 0);
+    for (int r = warp; r < rows; r += nwarps) {
+        float acc[ROUTE_TPB];
+#pragma unroll
+        for (int j = 0; j < ROUTE_TPB; ++j) acc[j] = 0.f;
+        const TW* wr = router + (size_t)r * H;
+        for (int i = lane; i < H; i += 32) {
+            const float w = to_float(wr[i]);
+#pragma unroll
+            for (int j = 0; j < ROUTE_TPB; ++j) acc[j] += w * hs[j * H + i];
+        }
+#pragma unroll
+        for (int j = 0; j < ROUTE_TPB; ++j) {
+            const float v = warp_sum(acc[j]);
+            if (lane == 0) sc[j * (E + 1) + r] = v;
+        }
+    }
+    __syncthreads();
+    const int gsz = E / n_groups;
+    for (int j = warp; j < nt; j += nwarps) {
+        const int t = t0 + j;
+        float* z = sc + j * (E + 1);
+        float* c = ch + j * E;
+        float* g = gs + j * n_groups;
+        float* k = kf + j * n_groups;
+        float* chosen = sel + j * top;
+        for (int e = lane; e < E; e += 32) {
+            const float s = 1.f / (1.f + expf(-z[e]));
+            z[e] = s;
+            c[e] = s + to_float(correction[e]);
+        }
+        if (has_gate && lane == 0) gate_out[t] = 1.f / (1.f + expf(-z[E]));
+        __syncwarp();
+        if (n_groups > 1) {
+            for (int gi = lane; gi < n_groups; gi += 32) {
+                float m1 = -INFINITY, m2 = -INFINITY;
+                for (int e = gi * gsz; e < (gi + 1) * gsz; ++e) {
+                    const float v = c[e];
+                    if (v > m1) { m2 = m1; m1 = v; }
+                    else if (v > m2) m2 = v;
+                }
+                g[gi] = gsz >= 2 ? m1 + m2 : m1;
+            }
+            __syncwarp();
+            for (int gi = lane; gi < n_groups; gi += 32) {
+                int rank = 0;
+                const float mine = g[gi];
+                for (int gj = 0; gj < n_groups; ++gj) rank += (g[gj] > mine || (g[gj] == mine && gj < gi)) ? 1 : 0;
+                k[gi] = rank < keep ? 1.f : 0.f;
+            }
+            __syncwarp();
+            for (int e = lane; e < E; e += 32)
+                if (k[e / gsz] == 0.f) c[e] = -INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32) {
+            int rank = 0;
+            const float mine = c[e];
+            for (int f = 0; f < E; ++f) rank += (c[f] > mine || (c[f] == mine && f < e)) ? 1 : 0;
+            if (rank < top) {
+                idx[(size_t)t * top + rank] = e;
+                chosen[rank] = z[e];
+            }
+        }
+        __syncwarp();
+        float sum = 0.f;
+        for (int r = 0; r < top; ++r) sum += chosen[r];
+        for (int r = lane; r < top; r += 32) wts[(size_t)t * top + r] = chosen[r] / (sum + 1e-20f) * scale;
+    }
+}
+
+// y: [T, H] (row pitch ldy); router: [E (+1), H], row E the shared expert's gate when has_gate; correction: [E].
+// idx: [T, top] int, wts: [T, top] float, gate_out: [T] float (sigmoid of the gate row's sum).
+CELLM_API int cellm_route(int* idx, float* wts, float* gate_out, const void* y, long long ldy, const void* router, int w_dtype,
+                          const void* correction, int c_dtype, int T, int H, int E, int top, int n_groups, int keep, float scale,
+                          int has_gate, int act_dtype, cudaStream_t stream) {
+    if (T <= 0) return CELLM_OK;
+    if (E < 1 || top < 1 || top > E || n_groups < 1 || E % n_groups || keep < 1 || keep > n_groups || H < 1) return CELLM_ERR_SIZE;
+    if (has_gate && !gate_out) return CELLM_ERR_ARG;
+    if (w_dtype != act_dtype) return CELLM_ERR_DTYPE;
+    const size_t smem = ((size_t)ROUTE_TPB * (H + 2 * E + 1 + 2 * n_groups + top)) * sizeof(float);
+    if (smem > 200 * 1024) return CELLM_ERR_SIZE;
+    const unsigned blocks = (unsigned)((T + ROUTE_TPB - 1) / ROUTE_TPB);
+#define GO(TA, TC)                                                                                                          \
+    do {                                                                                                                    \
+        static size_t configured = 0;                                                                                       \
+        if (smem > 48 * 1024 && smem > configured) {                                                                        \
+            const cudaError_t e = cudaFuncSetAttribute(route_kernel<TA, TA, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            if (e != cudaSuccess) return (int)e;                                                                            \
+            configured = 200 * 1024;                                                                                        \
+        }                                                                                                                   \
+        CELLM_RUN((route_kernel<TA, TA, TC>), blocks, ROUTE_THREADS, smem, stream, idx, wts, gate_out, (const TA*)y, ldy,   \
+                  (const TA*)router, (const TC*)correction, T, H, E, top, n_groups, keep, scale, has_gate);                 \
+    } while (0)
+    if (act_dtype == CELLM_F32 && c_dtype == CELLM_F32) GO(float, float);
+    else if (act_dtype == CELLM_F32 && c_dtype == CELLM_BF16) GO(float, __nv_bfloat16);
+    else if (act_dtype == CELLM_BF16 && c_dtype == CELLM_F32) GO(__nv_bfloat16, float);
+    else if (act_dtype == CELLM_BF16 && c_dtype == CELLM_BF16) GO(__nv_bfloat16, __nv_bfloat16);
+    else return CELLM_ERR_DTYPE;
+#undef GO
+    return CELLM_OK;
+}
+
+// ---- the experts, row by row ----------------------------------------------------------------------------------------
+#define EXPERT_THREADS 128
+#define EXPERT_ROWS 32          // output rows a block forms
+
+// mid[t * top + k, :] = act(U_e y[t]) for e = idx[t, k]; up: [E * ff, H]
+template <typename TA>
+__global__ void __launch_bounds__(EXPERT_THREADS)
+expert_up_kernel(TA* __restrict__ mid, const TA* __restrict__ y, long long ldy, const TA* __restrict__ up, const int* __restrict__ idx,
+                 int H, int ff, int top, int E, int act) {
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slot = blockIdx.x, t = slot / top;
+    const bool vec = rows_vectorise(up, H, H);
+    pdl_trigger();
+    pdl_wait();
+    for (int i = threadIdx.x; i < H; i += EXPERT_THREADS) smem[i] = to_float(y[(size_t)t * ldy + i]);
+    int e = idx[slot];
+    e = min(max(e, 0), E - 1);
+    __syncthreads();
+    const int r_end = min(ff, (int)(blockIdx.y + 1) * EXPERT_ROWS);
+    for (int r = blockIdx.y * EXPERT_ROWS + warp; r < r_end; r += EXPERT_THREADS / 32) {
+        const float d = warp_sum(lane_dot<TA>(up + ((size_t)e * ff + r) * H, smem, H, lane, vec));
+        if (lane == 0) mid[(size_t)slot * ff + r] = from_float<TA>(cellm_activate(d, act));
+    }
+}
+
+// out[t, r] = sum_k wts[t, k] * (D_e mid[t * top + k])[r] (+ gate[t] * shared[t, r]); down: [E * H, ff]
+template <typename TA>
+__global__ void __launch_bounds__(EXPERT_THREADS)
+expert_down_kernel(TA* __restrict__ out, const TA* __restrict__ mid, const TA* __restrict__ down, const int* __restrict__ idx,
+                   const float* __restrict__ wts, const float* __restrict__ shared, const float* __restrict__ gate, int H, int ff, int top,
+                   int E) {
+    extern __shared__ float smem[];             // [top * ff] the token's middles, then [top] weights and experts
+    float* ms = smem;
+    float* wk = smem + (size_t)top * ff;
+    int* ek = (int*)(wk + top);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    const bool vec = rows_vectorise(down, ff, ff);
+    pdl_trigger();
+    pdl_wait();
+    for (int i = threadIdx.x; i < top * ff; i += EXPERT_THREADS) ms[i] = to_float(mid[(size_t)t * top * ff + i]);
+    for (int k = threadIdx.x; k < top; k += EXPERT_THREADS) {
+        wk[k] = wts[(size_t)t * top + k];
+        ek[k] = min(max(idx[(size_t)t * top + k], 0), E - 1);
+    }
+    __syncthreads();
+    const int r_end = min(H, (int)(blockIdx.y + 1) * EXPERT_ROWS);
+    for (int r = blockIdx.y * EXPERT_ROWS + warp; r < r_end; r += EXPERT_THREADS / 32) {
+        float a = 0.f;
+        for (int k = 0; k < top; ++k) a += wk[k] * lane_dot<TA>(down + ((size_t)ek[k] * H + r) * ff, ms + (size_t)k * ff, ff, lane, vec);
+        a = warp_sum(a);
+        if (lane == 0) {
+            if (shared) a += (gate ? gate[t] : 1.f) * shared[(size_t)t * H + r];
+            out[(size_t)t * H + r] = from_float<TA>(a);
+        }
+    }
+}
+
+// The chosen experts of every token, walked row by row. mid: [T * top, ff] scratch of the activations' type.
+// shared: [T, H] float, the shared expert's result before its gate (null: none); gate: [T] (null: the result as it is).
+CELLM_API int cellm_experts_rowwise(void* out, void* mid, const void* y, long long ldy, const void* up, const void* down, const int* idx,
+                                    const float* wts, const float* shared, const float* gate, int T, int H, int ff, int top, int E, int act,
+                                    int dtype, cudaStream_t stream) {
+    if (T <= 0) return CELLM_OK;
+    if (H < 1 || ff < 1 || top < 1 || E < 1) return CELLM_ERR_SIZE;
+    const size_t smem_up = (size_t)H * sizeof(float), smem_down = ((size_t)top * ff + 2 * top) * sizeof(float);
+    if (smem_up > 200 * 1024 || smem_down > 200 * 1024) return CELLM_ERR_SIZE;
+    const dim3 grid_up((unsigned)(T * top), (unsigned)((ff + EXPERT_ROWS - 1) / EXPERT_ROWS));
+    const dim3 grid_down((unsigned)T, (unsigned)((H + EXPERT_ROWS - 1) / EXPERT_ROWS));
+#define GO(TA)                                                                                                                    \
+    do {                                                                                                                          \
+        static bool configured = false;                                                                                           \
+        if (!configured && (smem_up > 48 * 1024 || smem_down > 48 * 1024)) {                                                      \
+            cudaError_t e = cudaFuncSetAttribute(expert_up_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);  \
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(expert_down_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            if (e != cudaSuccess) return (int)e;                                                                                  \
+            configured = true;                                                                                                    \
+        }                                                                                                                         \
+        CELLM_RUN(expert_up_kernel<TA>, grid_up, EXPERT_THREADS, smem_up, stream, (TA*)mid, (const TA*)y, ldy, (const TA*)up, idx, H, ff, top, E, act); \
+        CELLM_RUN(expert_down_kernel<TA>, grid_down, EXPERT_THREADS, smem_down, stream, (TA*)out, (const TA*)mid, (const TA*)down, idx, wts, \
+                  shared, gate, H, ff, top, E);                                                                                   \
+    } while (0)
+    if (dtype == CELLM_F32) GO(float);
+    else if (dtype == CELLM_BF16) GO(__nv_bfloat16);
+    else return CELLM_ERR_DTYPE;
+#undef GO
+    return CELLM_OK;
+}
+
+// ---- a plain activation: h = act(u) for 32-bit sums u [T, n] (row pitch ld) ----------------------------------------------
+template <typename T>
+__global__ void activation_kernel(T* __restrict__ h, const float* __restrict__ u, long long ld, int n, int act, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / n, c = i - t * n;
+    h[i] = from_float<T>(cellm_activate(u[t * ld + c], act));
+}
+
+CELLM_API int cellm_activation(void* h, const float* u, long long ld, int T, int n, int act, int dtype, cudaStream_t stream) {
+    if (T <= 0 || n <= 0) return CELLM_OK;
+    if (act < 0 || act > 3) return CELLM_ERR_ARG;
+    const size_t total = (size_t)T * n;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == CELLM_F32) CELLM_RUN(activation_kernel<float>, blocks, 256, 0, stream, (float*)h, u, ld, n, act, total);
+    else if (dtype == CELLM_BF16) CELLM_RUN(activation_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)h, u, ld, n, act, total);
+    else return CELLM_ERR_DTYPE;
+    return CELLM_OK;
+}

@@ -307,6 +307,7 @@ API long long cellm_exec_sizeof(int which) {
         case 17: return sizeof(cellm::MinGruParams);
         case 18: return sizeof(cellm::LatentAttentionParams);
         case 19: return sizeof(cellm::GatedMlpParams);
+        case 20: return sizeof(cellm::RoutedMlpParams);
         default: return -1;
     }
 }

@@ -52,7 +52,16 @@ typedef int (*BiasAddFn)(P out, CP in, CP b, int w_tag, int T, int N, int tag, P
 typedef int (*HeadProductMmaFn)(P out, i64 ldo, i64 out_hs, CP in, i64 ldi, i64 in_hs, CP w, int T, int heads, int N, int K, P stream);
 typedef int (*AttentionLatentFn)(P out, P part_o, P part_ml, CP q, CP pool, CP cu, CP ctx, CP bt, int bt_stride, int B, int T, int n_tiles,
                                  int pages, int page_size, int nh, int kw, int dv, float scale, int nsplit, P err, P stream);
-
+typedef int (*EmbedPosFn)(P out, CP table, int tag, CP ids, CP pos_table, CP positions, int max_pos, int T, int H, int V, float scale, P err,
+                          P stream);
+typedef int (*AttnPrepFn)(P q, CP qkv, i64 row_stride, CP q_w, CP k_w, int w_tag, float eps, int span, float temp_coef, int temp_every,
+                          CP positions, CP seq, CP bt, int bt_stride, P kp, P vp, int num_pages, int page_size, int T, int nh, int nkv,
+                          int hd, int hdv, int act_tag, P err, P stream);
+typedef int (*RouteFn)(P idx, P wts, P gate, CP y, i64 ldy, CP router, int w_tag, CP correction, int c_tag, int T, int H, int E, int top,
+                       int n_groups, int keep, float scale, int has_gate, int act_tag, P stream);
+typedef int (*ExpertsRowwiseFn)(P out, P mid, CP y, i64 ldy, CP up, CP down, CP idx, CP wts, CP shared, CP gate, int T, int H, int ff, int top,
+                                int E, int act, int tag, P stream);
+typedef int (*ActivationFn)(P h, CP u, i64 ld, int T, int n, int act, int tag, P stream);
 
 struct KernelError : std::runtime_error {
     int code;
@@ -218,6 +227,11 @@ struct Run {
     }
 
     void embed(const EmbedParams& e) {
+        if (e.pos_table)
+            LAUNCH(fn<EmbedPosFn>(FN_EMBED_POS)(regs.x, e.table, (int)e.dtype, s.ids, e.pos_table, s.positions, (int)e.max_pos, (int)s.T, (int)p.H,
+                                            (int)p.V, (float)e.scale, s.err, s.stream),
+               "embed_pos");
+        else
         LAUNCH(fn<EmbedFn>(FN_EMBED)(regs.x, e.table, (int)e.dtype, s.ids, (int)s.T, (int)p.H, (int)p.V, (float)e.scale, s.err, s.stream),
            "embed");
         stream_in_y = false;
@@ -296,6 +310,7 @@ struct Run {
 
     void feed_forward(const SwiGLUParams& L, const void* x, void* out);
     void gated_mlp(const GatedMlpParams& L, const void* x, void* out);
+    void routed_mlp(const RoutedMlpParams& L, const void* x, void* out);
     void mingru(const MinGruParams& L, const ExecItem& it, const void* x, void* out);
     void latent_attention(const LatentAttentionParams& L, const ExecItem& it, const void* x, void* out);
     void short_conv(const ShortConvParams& L, const ExecItem& it, const void* x, void* out);
@@ -315,6 +330,7 @@ struct Run {
                 break;
             case OP_SWIGLU: feed_forward(*static_cast<const SwiGLUParams*>(op.params), in, out); break;
             case OP_GATED_MLP: gated_mlp(*static_cast<const GatedMlpParams*>(op.params), in, out); break;
+            case OP_ROUTED_MLP: routed_mlp(*static_cast<const RoutedMlpParams*>(op.params), in, out); break;
             case OP_MINGRU:
                 if (!it) throw std::runtime_error("executor: a mixer outside the layers");
                 mingru(*static_cast<const MinGruParams*>(op.params), *it, in, out);
@@ -346,7 +362,7 @@ struct Run {
             case OP_PYTHON: python(*static_cast<const PythonParams*>(op.params)); break;
             case OP_READ_STREAM: read_stream(); break;
             case OP_GATED_NORM_ADD: gated_norm_add(*static_cast<const GatedNormAddParams*>(op.params)); break;
-            case OP_SHORT_CONV: case OP_ATTENTION: case OP_SWIGLU: case OP_MINGRU: case OP_LATENT_ATTENTION: case OP_GATED_MLP: {
+            case OP_SHORT_CONV: case OP_ATTENTION: case OP_SWIGLU: case OP_MINGRU: case OP_LATENT_ATTENTION: case OP_GATED_MLP: case OP_ROUTED_MLP: {
                 void* out = slot[turn];
                 produce(op, it, input(), out);
                 set_pending(out);
@@ -492,10 +508,10 @@ void Run::short_conv(const ShortConvParams& L, const ExecItem& it, const void* x
 }
 
 void* Run::attend(const AttentionParams& L, const ExecItem& it, const void* q, void* o) {
-    const i64 T = s.T, nh = L.nh, nkv = L.nkv, hd = L.hd;
-    if (!o) o = arena.take(T * nh * hd * elt(act));
+    const i64 T = s.T, nh = L.nh, nkv = L.nkv, hd = L.hd, hdv = L.hdv > 0 ? L.hdv : L.hd;
+    if (!o) o = arena.take(T * nh * hdv * elt(act));
     const float scale = (float)L.scale;
-    if (act == EXEC_BF16 && (hd == 32 || hd == 64 || hd == 128) && L.scale > 0) {
+    if (act == EXEC_BF16 && (hd == 32 || hd == 64 || hd == 128) && hdv == hd && L.scale > 0) {
         const i64 G = nh / nkv;
         if (s.max_q_len * G <= 16) {
             // decoded tokens: one CTA per (request, kv head, piece of the keys)
@@ -566,6 +582,13 @@ void* Run::attend(const AttentionParams& L, const ExecItem& it, const void* q, v
         return o;
     }
     // 32-bit, other head sizes: one block per (token, head) over the block table
+    if (hdv != hd) {
+        LAUNCH(fn<AttentionPlainFn>(FN_ATTENTION_PLAIN_WIDE)(o, q, it.k, it.v, s.positions, s.seq_of_token, it.block_table, (int)it.bt_stride,
+                                                         (int)it.num_pages, (int)it.page_size, (int)T, (int)nh, (int)nkv, (int)hd, (int)hdv,
+                                                         scale, (int)L.window, (int)act, s.err, s.stream),
+               "attention_plain_wide");
+        return o;
+    }
     LAUNCH(fn<AttentionPlainFn>(FN_ATTENTION_PLAIN)(o, q, it.k, it.v, s.positions, s.seq_of_token, it.block_table, (int)it.bt_stride,
                                                 (int)it.num_pages, (int)it.page_size, (int)T, (int)nh, (int)nkv, (int)hd, (int)hd, scale,
                                                 (int)L.window, (int)act, s.err, s.stream),
@@ -577,6 +600,24 @@ void Run::attention(const AttentionParams& L, const ExecItem& it, const void* x,
     const i64 T = s.T, H = p.H, nh = L.nh, hd = L.hd;
     const i64 nkv = it.writes ? L.nkv : 0;
     void* q = nullptr;
+    const i64 hdv = L.hdv > 0 ? L.hdv : hd;
+    if (hdv != hd || L.norm_whole || L.temp_coef != 0.0) {
+        // the general form: values of a width of their own, a norm over the whole projection, a query temperature
+        if (L.rot || L.inv_freq) throw std::runtime_error("executor: the general attention form has no rotation");
+        const i64 width = nh * hd + nkv * (hd + hdv);
+        void* qkv = linear(x, L.qkv, T, H, act, width);       // without a cache of its own: the query rows only
+        q = arena.take(T * nh * hd * elt(act));
+        const int span = L.q_norm_w ? (L.norm_whole ? 2 : 1) : 0;
+        LAUNCH(fn<AttnPrepFn>(FN_ATTN_PREP)(q, qkv, width, L.q_norm_w, L.k_norm_w, L.q_norm_w ? (int)L.qk_dtype : 0, (float)L.qk_eps, span,
+                                        (float)L.temp_coef, (int)L.temp_every, s.positions, s.seq_of_token,
+                                        nkv ? it.block_table : nullptr, nkv ? (int)it.bt_stride : 0, nkv ? it.k : nullptr,
+                                        nkv ? it.v : nullptr, nkv ? (int)it.num_pages : 0, (int)it.page_size, (int)T, (int)nh, (int)nkv,
+                                        (int)hd, (int)hdv, (int)act, s.err, s.stream),
+               "attn_prep");
+        void* o = attend(L, it, q);
+        product(out, o, L.out_proj, T, nh * hdv, act);
+        return;
+    }
     // decode steps, bfloat16, heads of 64 turned whole in the "half" layout, a cache of the item's own: the product,
     // the heads' norm, the rotation and the cache write as one kernel
     const bool rope_fused = p.fused_rope && s.max_q_len == 1 && it.writes && hd == 64 && act == EXEC_BF16 &&
@@ -622,6 +663,32 @@ void Run::gated_mlp(const GatedMlpParams& L, const void* x, void* out) {
     } else {
         product(out, h, L.down, T, L.ff, act);
     }
+}
+
+void Run::routed_mlp(const RoutedMlpParams& L, const void* x, void* out) {
+    const i64 T = s.T, H = p.H, e = elt(act);
+    if (L.up.dtype != act || L.down.dtype != act || L.router.dtype != act)
+        throw std::runtime_error("executor: experts whose element type differs from the activations'");
+    void* idx = arena.take(T * L.top * 4);
+    void* wts = arena.take(T * L.top * 4);
+    void* gate = L.shared_gate ? arena.take(T * 4) : nullptr;
+    LAUNCH(fn<RouteFn>(FN_ROUTE)(idx, wts, gate, x, H, L.router.w, (int)L.router.dtype, L.correction, (int)L.c_dtype, (int)T, (int)H,
+                             (int)L.experts, (int)L.top, (int)L.n_groups, (int)L.keep, (float)L.scale, L.shared_gate ? 1 : 0, (int)act,
+                             s.stream),
+           "route");
+    // the shared expert: two plain products around its activation; its result stays 32-bit until the experts' sum takes it
+    void* shared = nullptr;
+    if (L.shared_up.w) {
+        void* u = linear(x, L.shared_up, T, H, EXEC_F32);
+        void* h = arena.take(T * L.shared_ff * e);
+        LAUNCH(fn<ActivationFn>(FN_ACTIVATION)(h, u, L.shared_ff, (int)T, (int)L.shared_ff, (int)L.act, (int)act, s.stream), "activation");
+        shared = linear(h, L.shared_down, T, L.shared_ff, EXEC_F32);
+    }
+    void* mid = arena.take(T * L.top * L.ff * e);
+    LAUNCH(fn<ExpertsRowwiseFn>(FN_EXPERTS_ROWWISE)(out, mid, x, H, L.up.w, L.down.w, idx, wts, shared, gate, (int)T, (int)H, (int)L.ff,
+                                                (int)L.top, (int)L.experts, (int)L.act, (int)act, s.stream),
+           "experts_rowwise");
+    ++launches;         // up and down are a launch each
 }
 
 void Run::mingru(const MinGruParams& L, const ExecItem& it, const void* x, void* out) {

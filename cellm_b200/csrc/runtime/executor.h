@@ -52,7 +52,9 @@ enum OpKind : i64 {
     // pieces of the above by themselves, for exec_part only (the interpreter's kernel wrappers)
     OP_LINEAR, OP_ATTEND,
     // a layer whose sublayers read the stream itself and whose results join it through a gate and a norm
-    OP_READ_STREAM, OP_GATED_NORM_ADD, OP_MINGRU, OP_LATENT_ATTENTION, OP_GATED_MLP, OP_KINDS
+    OP_READ_STREAM, OP_GATED_NORM_ADD, OP_MINGRU, OP_LATENT_ATTENTION, OP_GATED_MLP,
+    // a feed-forward whose tokens each run a few of many small experts, chosen by a router
+    OP_ROUTED_MLP, OP_KINDS
 };
 
 struct ExecOp {
@@ -60,7 +62,8 @@ struct ExecOp {
     const void* params;     // the kind's parameter struct below
 };
 
-struct EmbedParams { const void* table; i64 dtype; double scale; };    // x = table[ids] * scale
+// x = table[ids] * scale (+ pos_table[positions], learned position vectors [max_pos, H] of the table's element type; null: none)
+struct EmbedParams { const void* table; i64 dtype; double scale; const void* pos_table; i64 max_pos; };
 struct RmsNormParams { const void* w; i64 dtype; double eps; i64 groups; };   // x += pending; y = rms_norm(x) * w (the mean over each of `groups` parts)
 struct ShortConvParams {
     ExecLinear in_proj, out_proj;
@@ -72,6 +75,10 @@ struct AttentionParams {
     i64 nh, nkv, hd, window; double scale;
     const void* q_norm_w; const void* k_norm_w; i64 qk_dtype; double qk_eps;
     i64 rot, interleaved; const void* inv_freq;     // rot = 0 with inv_freq null: no rotation
+    // The general form (attn_prep.cu), taken when any of these differs from its default; it has no rotation.
+    i64 hdv;                // width of a value head (0: hd); the item's pool of values has rows of this width
+    i64 norm_whole;         // 1: q and k are normed over all their heads at once (weights [nh * hd], [nkv * hd]); 0: per head
+    double temp_coef; i64 temp_every;       // q *= 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1); coef 0: none
 };
 struct SwiGLUParams {
     ExecLinear gate_up, down;
@@ -108,6 +115,18 @@ struct LatentAttentionParams {
 // down . (act(gate . y + bg) * (up . y + bu)) + bd; act 0 silu, 1 gelu (tanh form); the biases may be null.
 struct GatedMlpParams { ExecLinear gate_up, down; const void* bg; const void* bu; const void* bd; i64 b_dtype, ff, act, extra; };
 
+// Routed experts: out = sum over the token's `top` chosen experts of weight * down_e act(up_e y) (+ sigmoid(g . y) * shared(y)).
+// up: [experts * ff, H] and down: [experts * H, ff], the experts' matrices one below the other. router: [experts (+ 1), H], the
+// last row the shared expert's gate when it has one. The choice: see routed.cu. act: 0 gelu (erf), 1 gelu (tanh), 2 silu, 3 relu.
+struct RoutedMlpParams {
+    ExecLinear up, down, router;
+    const void* correction; i64 c_dtype;
+    i64 experts, top, n_groups, keep; double scale;
+    i64 ff, act;
+    ExecLinear shared_up, shared_down;      // w null: no shared expert
+    i64 shared_ff, shared_gate;
+};
+
 struct ExecOps { i64 n; const ExecOp* ops; };
 
 // The registers as a Python part sees and changes them.
@@ -126,7 +145,8 @@ typedef i64 (*PythonOpFn)(i64 token, ExecRegs* regs);
 enum ExecFn {
     FN_EMBED, FN_ADD_RMSNORM, FN_RESIDUAL_ADD, FN_SWIGLU, FN_SHORT_CONV, FN_QK_NORM_ROPE, FN_ATTENTION_PLAIN, FN_GEMM_PLAIN,
     FN_ATTENTION_DECODE, FN_ATTENTION_TC, FN_ATTENTION_FLASH, FN_GEMM_TCGEN05, FN_GEMM_CONV, FN_GEMM_ROPE,
-    FN_GATED_NORM_ADD, FN_STREAM_CAST, FN_MINGRU_SCAN, FN_LATENT_PREP, FN_HEAD_PRODUCT, FN_GATED_ACT, FN_BIAS_ADD, FN_ATTENTION_LATENT, FN_HEAD_PRODUCT_MMA, FN_COUNT
+    FN_GATED_NORM_ADD, FN_STREAM_CAST, FN_MINGRU_SCAN, FN_LATENT_PREP, FN_HEAD_PRODUCT, FN_GATED_ACT, FN_BIAS_ADD, FN_ATTENTION_LATENT, FN_HEAD_PRODUCT_MMA,
+    FN_EMBED_POS, FN_ATTN_PREP, FN_ATTENTION_PLAIN_WIDE, FN_ROUTE, FN_EXPERTS_ROWWISE, FN_ACTIVATION, FN_COUNT
 };
 
 struct ExecProgram {

@@ -19,6 +19,7 @@ _ERRORS = {-1: "unsupported element type", -2: "a size this kernel does not take
 _SIGNATURES = {
     "kernels_common": {
         "cellm_embed": [P, P, I, P, I, I, I, F, P, P],
+        "cellm_embed_pos": [P, P, I, P, P, P, I, I, I, I, F, P, P],
         "cellm_upload": [P, P, L, P],
         "cellm_add_rmsnorm": [P, P, P, I, P, P, I, I, I, F, I, P],
         "cellm_residual_add": [P, P, L, I, P],
@@ -33,6 +34,11 @@ _SIGNATURES = {
         "cellm_head_product": [P, L, L, P, L, L, P, I, I, I, I, I, P],
         "cellm_gated_act": [P, P, L, P, P, I, I, I, I, I, I, P],
         "cellm_bias_add": [P, P, P, I, I, I, I, P],
+        "cellm_attn_prep": [P, P, L, P, P, I, F, I, F, I, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, P],
+        "cellm_attention_plain_wide": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P],
+        "cellm_route": [P, P, P, P, L, P, I, P, I, I, I, I, I, I, I, F, I, I, P],
+        "cellm_experts_rowwise": [P, P, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
+        "cellm_activation": [P, P, L, I, I, I, I, P],
         "cellm_argmax": [P, P, I, I, P, P],
         "cellm_take_pending_tokens": [P, P, P, P, I, I, P, P],
         "cellm_keep_last_tokens": [P, P, P, I, I, P],

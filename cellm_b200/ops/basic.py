@@ -9,11 +9,19 @@ from ._lib import check, count_launch, fn, ptr, require_cuda, stream_of, tag
 _LIB = "kernels_common"
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, err: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
-    """Rows of `table` [V, H] for int32 ids [T], times `scale`, as float32 [T, H]."""
-    require_cuda(table, ids, err)
+def embed(table: torch.Tensor, ids: torch.Tensor, err: torch.Tensor, scale: float = 1.0,
+          pos_table: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rows of `table` [V, H] for int32 ids [T], times `scale`, as float32 [T, H]; with `pos_table` [P, H] (of the
+    table's element type) and int32 `positions` [T], plus the rows of that table (unscaled)."""
+    require_cuda(table, ids, err, pos_table, positions)
     T, (V, H) = ids.numel(), table.shape
     out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    if pos_table is not None:
+        if pos_table.dtype != table.dtype or pos_table.shape[1] != H or positions is None or positions.numel() != T:
+            raise ValueError("embed: position vectors [P, H] of the table's element type and one position per token")
+        check(fn(_LIB, "cellm_embed_pos")(ptr(out), ptr(table), tag(table), ptr(ids), ptr(pos_table), ptr(positions), pos_table.shape[0],
+                                          T, H, V, float(scale), ptr(err), stream_of(table)), "embed_pos")
+        return out
     check(fn(_LIB, "cellm_embed")(ptr(out), ptr(table), tag(table), ptr(ids), T, H, V, float(scale), ptr(err),
                                   stream_of(table)), "embed")
     return out

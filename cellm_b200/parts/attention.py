@@ -1,7 +1,11 @@
 """Grouped-query attention mixer over the paged cache
 (crates/cellm-model/src/lfm.rs:418-601): q, k, v projections, RMSNorm of every
 q and k head, position encoding, keys and values written to the request's
-pages, softmax(q.k * scale) over all earlier keys (or a window), out_proj."""
+pages, softmax(q.k * scale) over all earlier keys (or a window), out_proj.
+
+Beyond the reference's form, as parameters: values of a width of their own (`value_dim`), the norm of q and k
+taken over the whole projection instead of per head (`qk_norm_span`: "projection"), and a query temperature
+that grows with the position, q *= 1 + coef * ln(floor((pos + 1) / every) + 1) (`query_temperature`)."""
 from __future__ import annotations
 
 import torch
@@ -17,25 +21,30 @@ class AttentionMixer(Mixer):
     graph_safe = True
 
     """params: hidden_size, num_heads, num_kv_heads, head_dim, scale, window,
-    qk_norm (PartSpec of a norm over head_dim, or None), position (PartSpec or None).
-    weights: q_proj [nh*hd, H], k_proj, v_proj [nkv*hd, H], out_proj [H, nh*hd],
-    q_norm, k_norm [hd] if qk_norm."""
+    qk_norm (PartSpec of a norm over head_dim, or None), position (PartSpec or None),
+    value_dim (default head_dim), qk_norm_span ("head", the default, or "projection"),
+    query_temperature ({"coef", "every"} or None).
+    weights: q_proj [nh*hd, H], k_proj [nkv*hd, H], v_proj [nkv*vd, H], out_proj [H, nh*vd],
+    q_norm, k_norm [hd] if qk_norm ([nh*hd] and [nkv*hd] when its span is the projection)."""
 
     can_read_foreign_cache = True
 
     @classmethod
     def weight_specs(cls, params):
         H, nh, nkv, hd = params["hidden_size"], params["num_heads"], params["num_kv_heads"], params["head_dim"]
+        vd = params.get("value_dim") or hd
         specs = {"q_proj": TensorSpec((nh * hd, H), "linear"), "k_proj": TensorSpec((nkv * hd, H), "linear"),
-                 "v_proj": TensorSpec((nkv * hd, H), "linear"), "out_proj": TensorSpec((H, nh * hd), "linear")}
+                 "v_proj": TensorSpec((nkv * vd, H), "linear"), "out_proj": TensorSpec((H, nh * vd), "linear")}
         if params.get("qk_norm") is not None:
-            specs["q_norm"] = TensorSpec((hd,), "norm")
-            specs["k_norm"] = TensorSpec((hd,), "norm")
+            whole = params.get("qk_norm_span", "head") == "projection"
+            specs["q_norm"] = TensorSpec((nh * hd if whole else hd,), "norm")
+            specs["k_norm"] = TensorSpec((nkv * hd if whole else hd,), "norm")
         return specs
 
     @classmethod
     def cache_need(cls, params):
-        return PagedKV(int(params["num_kv_heads"]), int(params["head_dim"]), int(params.get("window", 0)))
+        hd, vd = int(params["head_dim"]), int(params.get("value_dim") or params["head_dim"])
+        return PagedKV(int(params["num_kv_heads"]), hd, int(params.get("window", 0)), value_dim=vd if vd != hd else 0)
 
     def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
         self.H = int(params["hidden_size"])
@@ -44,6 +53,20 @@ class AttentionMixer(Mixer):
             raise ConfigError(f"attention: {self.nh} heads are not a multiple of {self.nkv} key/value heads")
         self.scale = float(params["scale"])
         self.window = int(params.get("window", 0))
+        self.vd = int(params.get("value_dim") or self.hd)
+        span = params.get("qk_norm_span", "head")
+        if span not in ("head", "projection"):
+            raise ConfigError(f"attention: qk_norm_span {span!r}; known: 'head', 'projection'")
+        self.norm_whole = span == "projection" and params.get("qk_norm") is not None
+        temp = params.get("query_temperature")
+        self.temp_coef, self.temp_every = (float(temp["coef"]), int(temp["every"])) if temp else (0.0, 1)
+        if self.temp_every < 1:
+            raise ConfigError(f"attention: query_temperature.every must be positive, not {self.temp_every}")
+        # what only the general kernels take (no rotation there)
+        self.general = self.vd != self.hd or self.norm_whole or self.temp_coef != 0.0
+        if self.general and params.get("position") is not None:
+            raise ConfigError("attention: a position encoding together with value_dim, a norm over the projection or a "
+                              "query temperature is not built")
         self.dtype = dtype
         dev = weights["q_proj"].device
         self.qkv = Linear(stack_rows(weights["q_proj"], weights["k_proj"], weights["v_proj"]), dtype)
@@ -83,6 +106,8 @@ class AttentionMixer(Mixer):
         from ..runtime import records as R
         p = R.AttentionParams()
         p.nh, p.nkv, p.hd, p.window, p.scale = self.nh, self.nkv, self.hd, self.window, self.scale
+        p.hdv = self.vd if self.vd != self.hd else 0
+        p.norm_whole, p.temp_coef, p.temp_every = int(self.norm_whole), self.temp_coef, self.temp_every
         return p
 
     def emit(self, emitter) -> None:
@@ -98,6 +123,8 @@ class AttentionMixer(Mixer):
         rec = self.record()
         if rec is not None:
             return part_program(self.dtype, x.device, self.H).run_part(rec, x, ctx, cache)
+        if self.general:
+            raise ConfigError("attention: the general form runs as a native record only (matrices of the activations' element type)")
         nh, nkv, hd = self.nh, (self.nkv if cache.writes else 0), self.hd
         bt, kp, vp = (cache.block_table, cache.k, cache.v) if nkv else (None, None, None)
         qkv = self.qkv(x) if cache.writes else self.q_only(x)

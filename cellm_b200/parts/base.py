@@ -32,7 +32,7 @@ import torch
 @dataclass(frozen=True)
 class TensorSpec:
     shape: tuple[int, ...]
-    init: str                    # "linear", "embedding", "norm", "conv_tap", "bias"
+    init: str                    # "linear", "embedding", "norm", "norm_offset" (around zero), "conv_tap", "bias"
     optional: bool = False
 
 
@@ -42,11 +42,13 @@ class PagedKV:
     """Keys and values that grow with the sequence, kept in pages.
     window = 0: all keys are kept; window = w: a token reads its last w keys.
     values = False: the rows serve as keys and values at once (a compressed cache whose values are a part
-    of the key rows): only the pool of keys exists."""
+    of the key rows): only the pool of keys exists.
+    value_dim = 0: value rows are as wide as key rows; otherwise the pool of values has rows of this width."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
     values: bool = True
+    value_dim: int = 0
 
 
 @dataclass(frozen=True)

@@ -26,6 +26,34 @@ class PreNormBlock(Block):
 register_block("pre_norm", PreNormBlock)
 
 
+class ParallelBlock(Block):
+    """A layer with one norm whose output both sublayers read: h = norm(x); x += mixer(h) + feed_forward(h).
+    The layer may have no feed-forward. Both results wait as addends of the 32-bit stream; the next norm adds them."""
+    graph_safe = True
+
+    def __init__(self, mixer_norm, mixer, feed_forward_norm, feed_forward):
+        from ..config.errors import ConfigError
+        if feed_forward_norm is not None:
+            raise ConfigError("parallel: the layer has one norm; its feed-forward reads the mixer's input")
+        self.mixer_norm, self.mixer = mixer_norm, mixer
+        self.feed_forward_norm, self.feed_forward = None, feed_forward
+
+    def emit(self, emitter) -> None:
+        self.mixer_norm.emit(emitter)
+        self.mixer.emit(emitter)
+        if self.feed_forward is not None:
+            self.feed_forward.emit(emitter)
+
+    def forward(self, residual: Residual, ctx: StepContext, cache: CacheBinding) -> None:
+        h = self.mixer_norm.forward(residual)
+        residual.add(self.mixer.forward(h, ctx, cache))
+        if self.feed_forward is not None:
+            residual.add(self.feed_forward.forward(h, ctx))
+
+
+register_block("parallel", ParallelBlock)
+
+
 class GatedPostNormBlock(Block):
     """A layer whose sublayers read the residual stream itself and whose norm sits on the sublayer's result:
 

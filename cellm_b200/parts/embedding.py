@@ -15,23 +15,31 @@ from .registry import register_embedding, register_head
 class TokenEmbedding(Embedding):
     graph_safe = True
 
-    """params: vocab_size, dim, scale (default 1: the row as it is). weights: weight [vocab, dim]."""
+    """params: vocab_size, dim, scale (default 1: the row as it is), max_positions (default 0: none; else a table of
+    learned position vectors is added, unscaled). weights: weight [vocab, dim], positions [max_positions, dim]."""
 
     @classmethod
     def weight_specs(cls, params):
-        return {"weight": TensorSpec((params["vocab_size"], params["dim"]), "embedding")}
+        specs = {"weight": TensorSpec((params["vocab_size"], params["dim"]), "embedding")}
+        if params.get("max_positions"):
+            specs["positions"] = TensorSpec((params["max_positions"], params["dim"]), "embedding")
+        return specs
 
     def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
         self.weight = weights["weight"].contiguous()
         self.scale = float(params.get("scale", 1.0))
+        self.positions = None
+        if params.get("max_positions"):
+            self.positions = weights["positions"].to(self.weight.dtype).contiguous()
 
     def emit(self, emitter) -> None:
         from ..ops._lib import tag
         from ..runtime import records as R
-        emitter.native(R.EMBED, R.EmbedParams(self.weight.data_ptr(), tag(self.weight), self.scale), part=self)
+        n = 0 if self.positions is None else self.positions.shape[0]
+        emitter.native(R.EMBED, R.EmbedParams(self.weight.data_ptr(), tag(self.weight), self.scale, R.ptr(self.positions), n), part=self)
 
     def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
-        return ops.embed(self.weight, token_ids, ctx.err, self.scale)
+        return ops.embed(self.weight, token_ids, ctx.err, self.scale, self.positions, ctx.positions if self.positions is not None else None)
 
 
 class LinearHead(Head):

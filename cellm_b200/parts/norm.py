@@ -1,6 +1,8 @@
 """RMSNorm (crates/cellm-kernels/src/cpu_kernels.rs:17-34): x / sqrt(mean(x^2) + eps) * w,
 fused with the addition of whatever waits to be added to the residual stream. With `groups` > 1 the
-vector is split into that many equal consecutive parts and each is divided by its own root mean square."""
+vector is split into that many equal consecutive parts and each is divided by its own root mean square.
+With `offset` c the stored weight lies around zero and the factor is c + w (formed once, in 32-bit, when the
+part is built: c + w has more digits than the stored type keeps)."""
 from __future__ import annotations
 
 from typing import Optional
@@ -16,11 +18,11 @@ from .registry import register_norm
 class RMSNorm(Norm):
     graph_safe = True
 
-    """params: dim, eps, groups (default 1). weights: weight [dim]."""
+    """params: dim, eps, groups (default 1), offset (default 0). weights: weight [dim]."""
 
     @classmethod
     def weight_specs(cls, params):
-        return {"weight": TensorSpec((params["dim"],), "norm")}
+        return {"weight": TensorSpec((params["dim"],), "norm_offset" if params.get("offset") else "norm")}
 
     def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
         self.dim = int(params["dim"])
@@ -28,7 +30,10 @@ class RMSNorm(Norm):
         self.groups = int(params.get("groups", 1))
         if self.groups < 1 or self.dim % self.groups:
             raise ConfigError(f"rms_norm: {self.dim} values do not split into {self.groups} equal groups")
+        self.offset = float(params.get("offset", 0.0))
         self.weight = weights["weight"].contiguous()
+        if self.offset:
+            self.weight = (self.weight.to(torch.float32) + self.offset).contiguous()
         self.dtype = dtype
 
     def emit(self, emitter) -> None:

@@ -20,7 +20,7 @@ I64, F64, PTR = c_longlong, c_double, c_void_p
 
 # record kinds, in the order of the executor's OpKind
 (EMBED, RMS_NORM, SHORT_CONV, ATTENTION, SWIGLU, HEAD, PYTHON, LINEAR, ATTEND,
- READ_STREAM, GATED_NORM_ADD, MINGRU, LATENT_ATTENTION, GATED_MLP) = range(14)
+ READ_STREAM, GATED_NORM_ADD, MINGRU, LATENT_ATTENTION, GATED_MLP, ROUTED_MLP) = range(15)
 
 
 class ExecLinear(Structure):
@@ -32,7 +32,7 @@ class ExecOp(Structure):
 
 
 class EmbedParams(Structure):
-    _fields_ = [("table", PTR), ("dtype", I64), ("scale", F64)]
+    _fields_ = [("table", PTR), ("dtype", I64), ("scale", F64), ("pos_table", PTR), ("max_pos", I64)]
 
 
 class RmsNormParams(Structure):
@@ -47,7 +47,8 @@ class ShortConvParams(Structure):
 class AttentionParams(Structure):
     _fields_ = [("qkv", ExecLinear), ("out_proj", ExecLinear), ("nh", I64), ("nkv", I64), ("hd", I64), ("window", I64),
                 ("scale", F64), ("q_norm_w", PTR), ("k_norm_w", PTR), ("qk_dtype", I64), ("qk_eps", F64),
-                ("rot", I64), ("interleaved", I64), ("inv_freq", PTR)]
+                ("rot", I64), ("interleaved", I64), ("inv_freq", PTR), ("hdv", I64), ("norm_whole", I64),
+                ("temp_coef", F64), ("temp_every", I64)]
 
 
 class SwiGLUParams(Structure):
@@ -89,6 +90,12 @@ class GatedMlpParams(Structure):
                 ("ff", I64), ("act", I64), ("extra", I64)]
 
 
+class RoutedMlpParams(Structure):
+    _fields_ = [("up", ExecLinear), ("down", ExecLinear), ("router", ExecLinear), ("correction", PTR), ("c_dtype", I64),
+                ("experts", I64), ("top", I64), ("n_groups", I64), ("keep", I64), ("scale", F64), ("ff", I64), ("act", I64),
+                ("shared_up", ExecLinear), ("shared_down", ExecLinear), ("shared_ff", I64), ("shared_gate", I64)]
+
+
 class ExecOps(Structure):
     _fields_ = [("n", I64), ("ops", POINTER(ExecOp))]
 
@@ -109,7 +116,10 @@ ENTRY_POINTS = [("kernels_common", "cellm_embed"), ("kernels_common", "cellm_add
                 ("kernels_common", "cellm_gated_norm_add"), ("kernels_common", "cellm_stream_cast"),
                 ("kernels_common", "cellm_mingru_scan"), ("kernels_common", "cellm_latent_prep"),
                 ("kernels_common", "cellm_head_product"), ("kernels_common", "cellm_gated_act"), ("kernels_common", "cellm_bias_add"),
-                ("attention_latent", "cellm_attention_latent"), ("attention_latent", "cellm_head_product_mma")]
+                ("attention_latent", "cellm_attention_latent"), ("attention_latent", "cellm_head_product_mma"),
+                ("kernels_common", "cellm_embed_pos"), ("kernels_common", "cellm_attn_prep"),
+                ("kernels_common", "cellm_attention_plain_wide"), ("kernels_common", "cellm_route"),
+                ("kernels_common", "cellm_experts_rowwise"), ("kernels_common", "cellm_activation")]
 # libraries a model whose activations are 32-bit never calls into (they need not be compiled for it)
 BF16_ONLY_LIBRARIES = ("attention_decode", "attention_tc", "attention_flash", "gemm_tcgen05", "attention_latent")
 # libraries that only records of these kinds reach (a program without such a record need not have them compiled)
@@ -142,7 +152,7 @@ class ExecStep(Structure):
 # in the order cellm_exec_sizeof() numbers them
 LAYOUT_CHECKED = (ExecLinear, ExecOp, ExecProgram, ExecItem, ExecStep, ExecRegs, EmbedParams, RmsNormParams, ShortConvParams,
                   AttentionParams, SwiGLUParams, HeadParams, PythonParams, ExecOps, LinearParams, ReadStreamParams, GatedNormAddParams,
-                  MinGruParams, LatentAttentionParams, GatedMlpParams)
+                  MinGruParams, LatentAttentionParams, GatedMlpParams, RoutedMlpParams)
 
 
 def ptr(t: Optional[torch.Tensor]):

@@ -41,6 +41,8 @@ def random_tensor(name: str, shape, init: str, seed: int, spec: InitSpec) -> tor
     g = _generator(seed, name)
     if init == "norm":
         return 1.0 + (torch.rand(shape, generator=g, dtype=torch.float32) * 2.0 - 1.0) * spec.norm_jitter
+    if init == "norm_offset":
+        return (torch.rand(shape, generator=g, dtype=torch.float32) * 2.0 - 1.0) * spec.norm_jitter
     std = {"linear": spec.linear_std, "embedding": spec.embedding_std, "conv_tap": spec.conv_tap_std,
            "bias": spec.bias_std}[init]
     return torch.randn(shape, generator=g, dtype=torch.float32) * std
