@@ -256,32 +256,53 @@ def matrix_bytes(model) -> int:
     return total
 
 
+def step_matrices(model, tokens: int):
+    """(bytes of the matrices a step of `tokens` tokens reads once, bytes of the matrices one token is multiplied with).
+    A routed feed-forward reads only the experts its tokens chose: of E experts with `top` chosen a token, a step is
+    expected to touch E * (1 - (1 - top / E) ** tokens) (random choices), and one token is multiplied with `top`."""
+    total = matrix_bytes(model)
+    step, token = float(total), float(total)
+    for blk in model.blocks:
+        ff = blk.feed_forward
+        if ff is not None and hasattr(ff, "E") and hasattr(ff, "top"):
+            experts = ff.up.untyped_storage().nbytes() + ff.down.untyped_storage().nbytes()
+            step -= experts * (1.0 - (1.0 - (1.0 - ff.top / ff.E) ** tokens))
+            token -= experts * (1.0 - ff.top / ff.E)
+    return step, token
+
+
+def design_shapes(design: str) -> dict:
+    from cellm_b200.config import presets
+    return {"vezalorn": presets.VEZALORN_SHAPES, "tufadra": presets.TUFADRA_SHAPES}[design]
+
+
 def compare_designs(args, rng) -> int:
     """Prefill (one 2,048-token prompt) and decode (batch 8 and 1 after 2,048-token prompts) of the new design and of
     LFM2 at equal sizes, device-timed with CUDA events through the step function."""
     import torch
     from cellm_b200 import write_random_model
-    from cellm_b200.config.presets import LFM2_SHAPES, VEZALORN_SHAPES
+    from cellm_b200.config.presets import LFM2_SHAPES
     from cellm_b200.models import load_model
     from cellm_b200.weights import InitSpec
     pk, pk_src = peaks()
     out = {}
     for size in [s for s in args.sizes.split(",") if s]:
-        shape, like = VEZALORN_SHAPES[size]
+        shape, like = design_shapes(args.design)[size]
         row = {}
         for name, config in ((args.design, shape), (like, LFM2_SHAPES[like])):
             with tempfile.TemporaryDirectory(prefix="cellm_bench_") as d:
                 write_random_model(d, config, seed=0, dtype="bfloat16", init=InitSpec(norm_jitter=0.0))
                 loaded = load_model(d, "bfloat16", "cuda:0")
             wbytes = matrix_bytes(loaded[2])
+            _, token_bytes = step_matrices(loaded[2], 1)
             pf_ms = time_prefill(loaded, rng)
-            r = {"matrix_gb": round(wbytes / 1e9, 3), "prefill_ms": round(pf_ms, 3),
+            r = {"matrix_gb": round(wbytes / 1e9, 3), "matrix_gb_a_token": round(token_bytes / 1e9, 3), "prefill_ms": round(pf_ms, 3),
                  "prefill_tok_s": round(PROMPT_LEN / (pf_ms * 1e-3), 1),
-                 "prefill_frac_of_bf16_peak": round(2 * PROMPT_LEN * (wbytes / 2) / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+                 "prefill_frac_of_bf16_peak": round(2 * PROMPT_LEN * (token_bytes / 2) / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
             for b in (args.batch, 1):
                 eng, ids = decode_setup(loaded, b, b * CONTEXT_LEN // PAGE, rng)
                 ms, e2e_ms, launches, _, _, ctx = time_decode(eng, ids, args.steps, args.warmup, rng)
-                step_bytes = wbytes + b * (ctx - args.steps / 2) * eng.cache.bytes_per_token()
+                step_bytes = step_matrices(loaded[2], b)[0] + b * (ctx - args.steps / 2) * eng.cache.bytes_per_token()
                 r[f"decode_b{b}"] = {"ms": round(ms, 4), "tok_s": round(b / (ms * 1e-3), 1), "e2e_ms": round(e2e_ms, 4),
                                      "launches": int(launches),
                                      "hbm_frac": round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
@@ -307,7 +328,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 runs")
-    ap.add_argument("--design", default=None, choices=["vezalorn"],
+    ap.add_argument("--design", default=None, choices=["vezalorn", "tufadra"],
                     help="instead of the default workload: prefill and decode throughput of this design at a few sizes, "
                          "beside LFM2 at equal width, depth and feed-forward (random weights); prints one JSON line")
     ap.add_argument("--sizes", default="700m,1.2b", help="with --design: which of the shapes to run")
@@ -341,8 +362,7 @@ def main() -> int:
     if args.design:
         if not args.profile_region:
             return compare_designs(args, rng)
-        from cellm_b200.config.presets import VEZALORN_SHAPES
-        config = VEZALORN_SHAPES[args.sizes.split(",")[0]][0]          # a profiler's region on the new design's first size
+        config = design_shapes(args.design)[args.sizes.split(",")[0]][0]          # a profiler's region on the new design's first size
     with tempfile.TemporaryDirectory(prefix="cellm_bench_") as d:
         # the benchmark's weights: N(0, 0.02), norm weights 1
         write_random_model(d, config, seed=0, dtype="bfloat16", init=InitSpec(norm_jitter=0.0))

@@ -52,3 +52,24 @@ VEZALORN_SHAPES = {
     "1.2b": (_vezalorn(2048, 16, [2, 5, 8, 10, 12, 14], 16, 8192), "lfm2-1.2b"),
     "700m": (_vezalorn(1536, 16, [2, 5, 8, 10, 12, 14], 12, 6912), "lfm2-700m"),
 }
+
+
+# ---- Tufadra shapes beside LFM2's ----------------------------------------------------------------------------------
+def _tufadra(width: int, layers: int, heads: int, kv_heads: int, experts: int, top: int, ff: int, shared_ff: int, vocab: int = 65536,
+             dim: int = 64, vdim: int = 64) -> dict:
+    """Layers of a width and count that an LFM2 shape has, every one an attention layer (the design has no other mixer)
+    with LFM2's heads beside a mixture of experts whose chosen experts and shared expert together are as wide as LFM2's
+    feed-forward."""
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "q_temp": {"coef": 0.1, "every": 1024}}
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "shared": {"ff": shared_ff},
+           "router": {"experts": experts, "top": top, "scale": 1.0, "groups": {"count": 8, "keep": 4}}}
+    return {"architecture": "Tufadra", "vocab": vocab, "width": width, "max_positions": 16384, "norm": {"eps": 1e-5},
+            "layers": [{"type": "attention", "mixer": dict(mixer), "mlp": dict(mlp)} for _ in range(layers)]}
+
+
+# name -> (Tufadra shape, the LFM2 shape of equal width and depth): 64 experts of which 6 are chosen, 6 x 1,024 + 2,048 = 8,192
+# active feed-forward columns at the larger size (LFM2-1.2B's feed-forward), 6 x 896 + 1,536 = 6,912 at the smaller
+TUFADRA_SHAPES = {
+    "1.2b": (_tufadra(2048, 16, 32, 8, 64, 6, 1024, 2048), "lfm2-1.2b"),
+    "700m": (_tufadra(1536, 16, 24, 8, 64, 6, 896, 1536), "lfm2-700m"),
+}

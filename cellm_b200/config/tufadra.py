@@ -149,14 +149,15 @@ class TufadraConfig:
                     raise ConfigError(f"config.json: {where}.mlp should be an object or null")
                 mlp = TufadraMoe.from_dict(mlp, where)
             layers.append(TufadraLayer(kind, mixer, mlp, src))
-        for i, layer in enumerate(layers):
-            j = layer.weights_of
-            if j is None:
-                continue
-            if layers[j].weights_of is not None:
-                raise ConfigError(f"config.json: layers[{i}]: weights_of names layer {j}, which has no tensors of its own")
-            if (layer.type, layer.mixer, layer.mlp) != (layers[j].type, layers[j].mixer, layers[j].mlp):
-                raise ConfigError(f"config.json: layers[{i}] uses the weights of layer {j} but has other sizes or constants")
+        for i, layer in enumerate(layers):           # a chain of references ends at the layer that has the tensors
+            j, seen = layer.weights_of, {i}
+            while j is not None and layers[j].weights_of is not None:
+                if j in seen:
+                    raise ConfigError(f"config.json: layers[{i}]: weights_of runs in a circle")
+                seen.add(j)
+                j = layers[j].weights_of
+            if j is not None:               # the sizes and constants are those of the layer whose tensors it uses
+                layers[i] = TufadraLayer(layers[j].type, layers[j].mixer, layers[j].mlp, j)
         c = cls(_get(d, "vocab", int), _get(d, "width", int), _get(d, "max_positions", int), _get(norm, "eps", float),
                 tuple(layers), _get(d, "eos_token_id", int, None))
         if c.vocab < 1 or c.width < 1 or c.max_positions < 1:

@@ -3,6 +3,7 @@
 //   all rows:       x[t] += delta[t];  y[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w
 //   selected rows:  v = x[rows[r]] + delta[rows[r]];  y[r] = v / sqrt(mean(v^2) + eps) * w
 //   groups > 1:     the mean is taken over each of `groups` equal consecutive parts of the row by itself
+//   two addends:    x[t] += delta[t] + delta2[t] (a layer whose two sublayers read the same norm's output)
 //
 // The residual stream x is 32-bit in every mode; sum and norm are 32-bit
 // (crates/cellm-kernels/src/cpu_kernels.rs:17-34 is the formula: the weight is
@@ -12,7 +13,7 @@
 #include "common.cuh"
 
 template <typename TA, typename TW>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ delta,
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ delta, const TA* __restrict__ delta2,
                                    const TW* __restrict__ w, TA* __restrict__ y,
                                    const int* __restrict__ rows, int H, int groups, float eps) {
     __shared__ float scratch[32];
@@ -22,6 +23,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
     const int t = rows ? rows[r] : r;
     float* xr = x + (size_t)t * H;
     const TA* dr = delta ? delta + (size_t)t * H : nullptr;
+    const TA* dr2 = (delta && delta2) ? delta2 + (size_t)t * H : nullptr;
     const bool write_back = (rows == nullptr) && (delta != nullptr);
     TA* yr = y + (size_t)r * H;
     // groups > 1: the row in equal consecutive parts, each divided by its own root mean square
@@ -31,7 +33,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
         float ss = 0.f;
         for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
             float v = xr[i];
-            if (dr) v += to_float(dr[i]);
+            if (dr) v += dr2 ? to_float(dr[i]) + to_float(dr2[i]) : to_float(dr[i]);
             if (write_back) xr[i] = v;
             ss += v * v;
         }
@@ -39,7 +41,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
         const float inv = 1.0f / sqrtf(ss / (float)Hg + eps);
         for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
             float v = xr[i];
-            if (dr && !write_back) v += to_float(dr[i]);
+            if (dr && !write_back) v += dr2 ? to_float(dr[i]) + to_float(dr2[i]) : to_float(dr[i]);
             yr[i] = from_float<TA>(v * inv * to_float(w[i]));
         }
     }
@@ -51,7 +53,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
 // the same order whatever the batch (thread partials of 8, then the block tree).
 template <typename TW>
 __global__ void add_rmsnorm_vec8_kernel(float* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
-                                        const TW* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                                        const __nv_bfloat16* __restrict__ delta2, const TW* __restrict__ w, __nv_bfloat16* __restrict__ y,
                                         const int* __restrict__ rows, int H, float eps) {
     __shared__ float scratch[32];
     pdl_trigger();
@@ -68,7 +70,18 @@ __global__ void add_rmsnorm_vec8_kernel(float* __restrict__ x, const __nv_bfloat
         const float4 a = *reinterpret_cast<const float4*>(x + (size_t)t * H + i0);
         const float4 b = *reinterpret_cast<const float4*>(x + (size_t)t * H + i0 + 4);
         v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-        if (delta) {
+        if (delta && delta2) {
+            const uint4 d = *reinterpret_cast<const uint4*>(delta + (size_t)t * H + i0);
+            const uint4 e = *reinterpret_cast<const uint4*>(delta2 + (size_t)t * H + i0);
+            const __nv_bfloat162* dp = reinterpret_cast<const __nv_bfloat162*>(&d);
+            const __nv_bfloat162* ep = reinterpret_cast<const __nv_bfloat162*>(&e);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(dp[j]), g = __bfloat1622float2(ep[j]);
+                v[2 * j] += f.x + g.x;
+                v[2 * j + 1] += f.y + g.y;
+            }
+        } else if (delta) {
             const uint4 d = *reinterpret_cast<const uint4*>(delta + (size_t)t * H + i0);
             const __nv_bfloat162* dp = reinterpret_cast<const __nv_bfloat162*>(&d);
 #pragma unroll
@@ -102,27 +115,28 @@ __global__ void add_rmsnorm_vec8_kernel(float* __restrict__ x, const __nv_bfloat
     }
 }
 
-// x: [*, H] float; delta: [*, H] act dtype or null; w: [H]; y: [n_rows, H] act dtype;
+// x: [*, H] float; delta, delta2: [*, H] act dtype or null (delta2 only beside delta); w: [H]; y: [n_rows, H] act dtype;
 // rows: null (all n_rows rows, x updated in place) or n_rows row indices (x left as is).
-CELLM_API int cellm_add_rmsnorm(float* x, const void* delta, const void* w, int w_dtype, void* y,
-                                const int* rows, int n_rows, int H, int groups, float eps, int act_dtype,
-                                cudaStream_t stream) {
+static int add_rmsnorm_impl(float* x, const void* delta, const void* delta2, const void* w, int w_dtype, void* y,
+                            const int* rows, int n_rows, int H, int groups, float eps, int act_dtype,
+                            cudaStream_t stream) {
     if (n_rows <= 0) return CELLM_OK;
+    if (delta2 && !delta) return CELLM_ERR_ARG;
     if (groups < 1 || H % groups) return CELLM_ERR_SIZE;
-    if (groups == 1 && act_dtype == CELLM_BF16 && (H & 7) == 0 && H <= 8192 && (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)y) & 15) == 0) {
+    if (groups == 1 && act_dtype == CELLM_BF16 && (H & 7) == 0 && H <= 8192 && (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)delta2 | (uintptr_t)y) & 15) == 0) {
         const int vthreads = ((H / 8 + 31) / 32) * 32;
         if (w_dtype == CELLM_BF16)
             CELLM_RUN(add_rmsnorm_vec8_kernel<__nv_bfloat16>, n_rows, vthreads, 0, stream, x, (const __nv_bfloat16*)delta,
-                      (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rows, H, eps);
+                      (const __nv_bfloat16*)delta2, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rows, H, eps);
         else if (w_dtype == CELLM_F32)
             CELLM_RUN(add_rmsnorm_vec8_kernel<float>, n_rows, vthreads, 0, stream, x, (const __nv_bfloat16*)delta,
-                      (const float*)w, (__nv_bfloat16*)y, rows, H, eps);
+                      (const __nv_bfloat16*)delta2, (const float*)w, (__nv_bfloat16*)y, rows, H, eps);
         else return CELLM_ERR_DTYPE;
         return CELLM_OK;
     }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
 #define LAUNCH(TA, TW) \
-    CELLM_RUN((add_rmsnorm_kernel<TA, TW>), n_rows, threads, 0, stream, x, (const TA*)delta, (const TW*)w, (TA*)y, rows, H, groups, eps)
+    CELLM_RUN((add_rmsnorm_kernel<TA, TW>), n_rows, threads, 0, stream, x, (const TA*)delta, (const TA*)delta2, (const TW*)w, (TA*)y, rows, H, groups, eps)
     if (act_dtype == CELLM_F32 && w_dtype == CELLM_F32) LAUNCH(float, float);
     else if (act_dtype == CELLM_F32 && w_dtype == CELLM_BF16) LAUNCH(float, __nv_bfloat16);
     else if (act_dtype == CELLM_BF16 && w_dtype == CELLM_F32) LAUNCH(__nv_bfloat16, float);
@@ -130,6 +144,20 @@ CELLM_API int cellm_add_rmsnorm(float* x, const void* delta, const void* w, int 
     else return CELLM_ERR_DTYPE;
 #undef LAUNCH
     return CELLM_OK;
+}
+
+CELLM_API int cellm_add_rmsnorm(float* x, const void* delta, const void* w, int w_dtype, void* y,
+                                const int* rows, int n_rows, int H, int groups, float eps, int act_dtype,
+                                cudaStream_t stream) {
+    return add_rmsnorm_impl(x, delta, nullptr, w, w_dtype, y, rows, n_rows, H, groups, eps, act_dtype, stream);
+}
+
+// Two addends that wait at once (either may be null; the sum delta + delta2 is formed first, then added to x).
+CELLM_API int cellm_add2_rmsnorm(float* x, const void* delta, const void* delta2, const void* w, int w_dtype, void* y,
+                                 const int* rows, int n_rows, int H, int groups, float eps, int act_dtype,
+                                 cudaStream_t stream) {
+    if (!delta) { delta = delta2; delta2 = nullptr; }
+    return add_rmsnorm_impl(x, delta, delta2, w, w_dtype, y, rows, n_rows, H, groups, eps, act_dtype, stream);
 }
 
 // Adds a pending delta into the residual stream without a norm (used when a

@@ -8,7 +8,9 @@
 //   q <- q * (1 + coef * ln(floor((pos + 1) / every) + 1))     (coef = 0: no temperature)
 //
 // Norm, temperature and positions are 32-bit. Rows of the projection: [nh * hd | nkv * hd | nkv * hdv].
-// Cache layout of one layer: keys [page][kv_head][slot in page][hd], values [page][kv_head][slot in page][hdv].
+// Cache layout of one layer: keys [page][kv_head][slot in page][hq], values [page][kv_head][slot in page][hv], where
+// hq >= hd and hv >= hdv are the widths the rows are kept in: a head padded with zeros to a width the fast attention
+// kernels take gives the same scores (the zeros add nothing) and values whose last columns are zero.
 #include "common.cuh"
 
 #define PREP_THREADS 256
@@ -19,7 +21,7 @@ attn_prep_kernel(TA* __restrict__ q_out, const TA* __restrict__ qkv, long long r
                  const TW* __restrict__ k_w, float eps, int span, float temp_coef, int temp_every,
                  const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
                  int bt_stride, TA* __restrict__ k_pool, TA* __restrict__ v_pool, int num_pages, int page_size, int nh, int nkv,
-                 int hd, int hdv, int* __restrict__ err) {
+                 int hd, int hdv, int hq, int hv, int* __restrict__ err) {
     extern __shared__ float smem[];          // [nh + nkv] a head's sum of squares, then its factor
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = PREP_THREADS / 32;
     pdl_trigger();
@@ -65,36 +67,50 @@ attn_prep_kernel(TA* __restrict__ q_out, const TA* __restrict__ qkv, long long r
         __syncthreads();
     }
     // queries
-    for (int i = threadIdx.x; i < nh * hd; i += PREP_THREADS) {
-        float v = to_float(row[i]);
-        if (span != 0) v = v * smem[i / hd] * to_float(q_w[span == 2 ? i : i % hd]);
-        q_out[(size_t)t * nh * hd + i] = from_float<TA>(v * temp);
+    for (int o = threadIdx.x; o < nh * hq; o += PREP_THREADS) {
+        const int h = o / hq, c = o - h * hq;
+        float v = 0.f;
+        if (c < hd) {
+            const int i = h * hd + c;
+            v = to_float(row[i]);
+            if (span != 0) v = v * smem[h] * to_float(q_w[span == 2 ? i : c]);
+            v *= temp;
+        }
+        q_out[(size_t)t * nh * hq + o] = from_float<TA>(v);
     }
     if (page < 0) return;
     const int slot = pos % page_size;
     // keys
     const TA* krow = row + (size_t)nh * hd;
-    for (int i = threadIdx.x; i < nkv * hd; i += PREP_THREADS) {
-        const int h = i / hd, c = i - h * hd;
-        float v = to_float(krow[i]);
-        if (span != 0) v = v * smem[nh + h] * to_float(k_w[span == 2 ? i : c]);
-        k_pool[((size_t)page * nkv + h) * page_size * hd + (size_t)slot * hd + c] = from_float<TA>(v);
+    for (int o = threadIdx.x; o < nkv * hq; o += PREP_THREADS) {
+        const int h = o / hq, c = o - h * hq;
+        float v = 0.f;
+        if (c < hd) {
+            const int i = h * hd + c;
+            v = to_float(krow[i]);
+            if (span != 0) v = v * smem[nh + h] * to_float(k_w[span == 2 ? i : c]);
+        }
+        k_pool[((size_t)page * nkv + h) * page_size * hq + (size_t)slot * hq + c] = from_float<TA>(v);
     }
     // values
     const TA* vrow = krow + (size_t)nkv * hd;
-    for (int i = threadIdx.x; i < nkv * hdv; i += PREP_THREADS) {
-        const int h = i / hdv, c = i - h * hdv;
-        v_pool[((size_t)page * nkv + h) * page_size * hdv + (size_t)slot * hdv + c] = vrow[i];
+    for (int o = threadIdx.x; o < nkv * hv; o += PREP_THREADS) {
+        const int h = o / hv, c = o - h * hv;
+        v_pool[((size_t)page * nkv + h) * page_size * hv + (size_t)slot * hv + c] = c < hdv ? vrow[h * hdv + c] : from_float<TA>(0.f);
     }
 }
 
-// qkv: [T, nh*hd + nkv*(hd + hdv)] (row pitch row_stride); q_out: [T, nh*hd]. nkv = 0: the rows hold queries only and
-// nothing is written. Weights: [hd] (span 1) or [nh*hd] and [nkv*hd] (span 2), null with span 0.
+// qkv: [T, nh*hd + nkv*(hd + hdv)] (row pitch row_stride); q_out: [T, nh*hq]. nkv = 0: the rows hold queries only and
+// nothing is written. Weights: [hd] (span 1) or [nh*hd] and [nkv*hd] (span 2), null with span 0. hq, hv: the widths
+// queries and keys, and values, are kept in (0: as they are).
 CELLM_API int cellm_attn_prep(void* q_out, const void* qkv, long long row_stride, const void* q_w, const void* k_w, int w_dtype, float eps,
                               int span, float temp_coef, int temp_every, const int* positions, const int* seq_of_token,
                               const int* block_table, int bt_stride, void* k_pool, void* v_pool, int num_pages, int page_size, int T,
-                              int nh, int nkv, int hd, int hdv, int dtype, int* err, cudaStream_t stream) {
+                              int nh, int nkv, int hd, int hdv, int hq, int hv, int dtype, int* err, cudaStream_t stream) {
     if (T <= 0) return CELLM_OK;
+    if (hq == 0) hq = hd;
+    if (hv == 0) hv = hdv;
+    if (hq < hd || hv < hdv) return CELLM_ERR_SIZE;
     if (nh < 1 || nkv < 0 || hd < 1 || hdv < 1 || span < 0 || span > 2) return CELLM_ERR_SIZE;
     if (span != 0 && (!q_w || (nkv > 0 && !k_w))) return CELLM_ERR_ARG;
     if (temp_coef != 0.f && temp_every < 1) return CELLM_ERR_ARG;
@@ -103,7 +119,7 @@ CELLM_API int cellm_attn_prep(void* q_out, const void* qkv, long long row_stride
 #define GO(TA, TW)                                                                                                           \
     CELLM_RUN((attn_prep_kernel<TA, TW>), T, PREP_THREADS, smem, stream, (TA*)q_out, (const TA*)qkv, row_stride, (const TW*)q_w, \
               (const TW*)k_w, eps, span, temp_coef, temp_every, positions, seq_of_token, block_table, bt_stride, (TA*)k_pool,  \
-              (TA*)v_pool, num_pages, page_size, nh, nkv, hd, hdv, err)
+              (TA*)v_pool, num_pages, page_size, nh, nkv, hd, hdv, hq, hv, err)
     if (dtype == CELLM_F32 && (w_dtype == CELLM_F32 || span == 0)) GO(float, float);
     else if (dtype == CELLM_F32 && w_dtype == CELLM_BF16) GO(float, __nv_bfloat16);
     else if (dtype == CELLM_BF16 && w_dtype == CELLM_F32) GO(__nv_bfloat16, float);

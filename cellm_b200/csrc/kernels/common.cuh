@@ -40,6 +40,16 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(f
     return __float2bfloat16_rn(v);
 }
 
+// Activations by number: 0 gelu (exact), 1 gelu (tanh form), 2 silu, 3 relu.
+__device__ __forceinline__ float cellm_activate(float z, int act) {
+    switch (act) {
+        case 0: return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));                    // gelu, exact
+        case 1: return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));   // gelu, tanh form
+        case 2: return z / (1.f + expf(-z));                                                 // silu
+        default: return fmaxf(z, 0.f);                                                       // relu
+    }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -667,11 +667,16 @@ template <> __device__ __forceinline__ void store_half_row<__nv_bfloat16>(__nv_b
 // buffered in tensor memory (2 x BN columns): while the epilogue warps drain one
 // buffer and store it, the MMA warp already fills the other, and the TMA warp keeps
 // the stage ring full across tile borders.
+//
+// Grouped form (tile_group given): W holds `groups` matrices of N rows one below the other, and every tile of 128
+// rows of A belongs to one of them, tile_group[row tile] (-1: the tile is empty and skipped by every role alike).
+// This is the product of tokens sorted by the expert they go to, each expert's run padded to whole tiles. act >= 0
+// applies that activation (common.cuh) to the sums before they are stored.
 template <int BN, int STAGES, int EPI, typename TO>
 __global__ void __launch_bounds__(192)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                                TO* __restrict__ C, int M, int N, int K, long long ldc, int w_is_static,
-                               int* __restrict__ err, int bn) {
+                               int* __restrict__ err, int bn, const int* __restrict__ tile_group, int act) {
     // bn: the width of a tile in columns, a multiple of 16 (of 128 with the SwiGLU epilogue) and at most BN, which
     // sizes the stages and the accumulators. Widths between the powers of two let the number of tiles come close
     // to a multiple of the SMs, so that the last wave is not half empty.
@@ -702,9 +707,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         if (lane == 0) {
             int it = 0;
             bool waited = false;
-            if (!w_is_static) { pdl_wait(); waited = true; }
+            if (!w_is_static || tile_group) { pdl_wait(); waited = true; }     // the tiles' groups are an earlier kernel's work
             for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
-                const int p0 = (tile % m_tiles) * BM, q0 = (tile / m_tiles) * bn;
+                const int grp = tile_group ? tile_group[tile % m_tiles] : 0;
+                if (grp < 0) continue;
+                const int p0 = (tile % m_tiles) * BM, q0 = (tile / m_tiles) * bn + grp * N;
                 int kb = 0;
                 if (!waited) {
                     // static weights: the ring's first loads of W go out before the wait on the preceding kernel
@@ -733,7 +740,9 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(BM, bn);
             int it = 0, tcount = 0;
-            for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
+            if (tile_group) pdl_wait();
+            for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
+                if (tile_group && tile_group[tile % m_tiles] < 0) continue;
                 const int buf = tcount & 1;
                 const uint32_t acc_phase = (uint32_t)(tcount >> 1) & 1u;
                 if (!mbar_wait(&sm.acc_empty2[buf], acc_phase ^ 1u, abort_flag)) { *abort_flag = 1; atomicOr(err, CELLM_DEV_WAIT_TIMEOUT); break; }
@@ -754,6 +763,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                 }
                 if (!ok) break;
                 umma_commit(&sm.acc_full2[buf]);
+                ++tcount;
             }
         }
     } else {
@@ -761,7 +771,9 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         const int pl = qtr * 32 + lane;
         bool waited = false;
         int tcount = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
+        if (tile_group) { pdl_wait(); waited = true; }
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            if (tile_group && tile_group[tile % m_tiles] < 0) continue;
             const int buf = tcount & 1;
             const uint32_t acc_phase = (uint32_t)(tcount >> 1) & 1u;
             if (!mbar_wait(&sm.acc_full2[buf], acc_phase, abort_flag)) {
@@ -784,6 +796,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                     if (cols == 32) tmem_ld32(lane_addr + (uint32_t)(c * 32), r);
                     else tmem_ld16(lane_addr + (uint32_t)(c * 32), r);
                     if (c == chunks - 1) { tc_fence_before(); mbar_arrive(&sm.acc_empty2[buf]); }
+                    if (act >= 0) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(cellm_activate(__uint_as_float(r[i]), act));
+                    }
                     const int q = q0 + c * 32;
                     if (p < M && q < N) {
                         if (cols == 32) store_row<TO>(C + (size_t)p * ldc + q, r, N - q, aligned);
@@ -809,6 +825,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                     }
                 }
             }
+            ++tcount;
         }
     }
     tc_fence_before();
@@ -855,7 +872,7 @@ int launch(const CUtensorMap& m_rows, const CUtensorMap& m_cols, TO* C, float* w
 
 template <int BN, int STAGES, int EPI, typename TO>
 int launch_persistent(const CUtensorMap& m_a, const CUtensorMap& m_w, TO* C, int M, int N, int K, long long ldc,
-                      int w_is_static, int* err, cudaStream_t stream, int bn) {
+                      int w_is_static, int* err, cudaStream_t stream, int bn, const int* tile_group = nullptr, int act = -1) {
     const size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
     static int sms = 0;
     if (sms == 0) {
@@ -869,7 +886,7 @@ int launch_persistent(const CUtensorMap& m_a, const CUtensorMap& m_w, TO* C, int
     const int tiles = ((N + bn - 1) / bn) * ((M + BM - 1) / BM);
     dim3 grid((unsigned)(tiles < sms ? tiles : sms));
     cudaError_t e = cellm_launch(gemm_tcgen05_persistent_kernel<BN, STAGES, EPI, TO>, grid, dim3(192), smem, stream, m_a,
-                                 m_w, C, M, N, K, ldc, w_is_static, err, bn);
+                                 m_w, C, M, N, K, ldc, w_is_static, err, bn, tile_group, act);
     return e == cudaSuccess ? CELLM_OK : (int)e;
 }
 
@@ -999,6 +1016,28 @@ static int gemm_impl(void* C, const void* A, const void* W, int M, int N, int K,
         else CELLM_RUN((splitk_sum_kernel<1, __nv_bfloat16>), blocks, 256, 0, stream, workspace, (__nv_bfloat16*)C, M, N, ldc, split);
     }
     return rc;
+}
+
+// The grouped product (see the persistent kernel): A [M, K] in tiles of 128 rows, tile i multiplied with matrix
+// tile_group[i] of W [groups * N, K]; C [M, N]. act: -1 none, else an activation on the sums.
+CELLM_API int cellm_gemm_grouped_tcgen05(void* C, const void* A, const void* W, int M, int N, int K, int groups, long long lda,
+                                         long long ldw, long long ldc, int out_dtype, const int* tile_group, int act, int* err,
+                                         cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return CELLM_OK;
+    if (K <= 0 || (K & 7) || groups < 1 || (M % BM)) return CELLM_ERR_SIZE;
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((lda * 2) & 15) || ((ldw * 2) & 15)) return CELLM_ERR_ALIGN;
+    if (out_dtype != CELLM_F32 && out_dtype != CELLM_BF16) return CELLM_ERR_DTYPE;
+    if (!tile_group || act > 3) return CELLM_ERR_ARG;
+    const int bn = N > 128 ? 256 : 128;
+    CUtensorMap map_a, map_w;
+    if (!tensor_map(&map_a, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, (uint32_t)BM)) return CELLM_ERR_ARG;
+    if (!tensor_map(&map_w, W, (uint64_t)groups * (uint64_t)N, (uint64_t)K, (uint64_t)ldw * 2, (uint32_t)bn)) return CELLM_ERR_ARG;
+    if (bn == 128) {
+        if (out_dtype == CELLM_F32) return launch_persistent<128, 6, 0, float>(map_a, map_w, (float*)C, M, N, K, ldc, 0, err, stream, bn, tile_group, act);
+        return launch_persistent<128, 6, 0, __nv_bfloat16>(map_a, map_w, (__nv_bfloat16*)C, M, N, K, ldc, 0, err, stream, bn, tile_group, act);
+    }
+    if (out_dtype == CELLM_F32) return launch_persistent<256, 4, 0, float>(map_a, map_w, (float*)C, M, N, K, ldc, 0, err, stream, bn, tile_group, act);
+    return launch_persistent<256, 4, 0, __nv_bfloat16>(map_a, map_w, (__nv_bfloat16*)C, M, N, K, ldc, 0, err, stream, bn, tile_group, act);
 }
 
 // The product described above gemm_impl.

@@ -12,17 +12,7 @@
 // that depends on the sizes alone, so a token's result does not depend on what else is in the batch.
 #include "common.cuh"
 
-#define ROUTE_TPB 8
 #define ROUTE_THREADS 128
-
-__device__ __forceinline__ float cellm_activate(float z, int act) {
-    switch (act) {
-        case 0: return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));                    // gelu, exact
-        case 1: return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));   // gelu, tanh form
-        case 2: return z / (1.f + expf(-z));                                                 // silu
-        default: return fmaxf(z, 0.f);                                                       // relu
-    }
-}
 
 // A lane's share of the dot product of a weight row with a vector held as floats: pieces of 16 bytes where the
 // row allows it (`vec`), else element by element.
@@ -66,9 +56,9 @@ template <typename TW> __device__ __forceinline__ bool rows_vectorise(const TW* 
 }
 
 // ---- the router ----------------------------------------------------------------------------------------------------
-// One block takes ROUTE_TPB tokens: their inputs lie in shared memory, a warp forms one router row's sums for all of
+// One block takes ROUTE_TPB tokens (8, or 1 where eight rows of the input do not fit shared memory): their inputs lie in shared memory, a warp forms one router row's sums for all of
 // them at once, then a warp a token chooses.
-template <typename TA, typename TW, typename TC>
+template <int ROUTE_TPB, typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(ROUTE_THREADS)
 route_kernel(int* __restrict__ idx, float* __restrict__ wts, float* __restrict__ gate_out, const TA* __restrict__ y, long long ldy,
              const TW* __restrict__ router, const TC* __restrict__ correction, int T, int H, int E, int top, int n_groups, int keep,
@@ -169,25 +159,33 @@ CELLM_API int cellm_route(int* idx, float* wts, float* gate_out, const void* y, 
     if (E < 1 || top < 1 || top > E || n_groups < 1 || E % n_groups || keep < 1 || keep > n_groups || H < 1) return CELLM_ERR_SIZE;
     if (has_gate && !gate_out) return CELLM_ERR_ARG;
     if (w_dtype != act_dtype) return CELLM_ERR_DTYPE;
-    const size_t smem = ((size_t)ROUTE_TPB * (H + 2 * E + 1 + 2 * n_groups + top)) * sizeof(float);
+    const size_t per_token = ((size_t)H + 2 * E + 1 + 2 * n_groups + top) * sizeof(float);
+    const int tpb = 8 * per_token <= 200 * 1024 ? 8 : 1;
+    const size_t smem = tpb * per_token;
     if (smem > 200 * 1024) return CELLM_ERR_SIZE;
-    const unsigned blocks = (unsigned)((T + ROUTE_TPB - 1) / ROUTE_TPB);
-#define GO(TA, TC)                                                                                                          \
+    const unsigned blocks = (unsigned)((T + tpb - 1) / tpb);
+#define GO2(TPB, TA, TC)                                                                                                    \
     do {                                                                                                                    \
         static size_t configured = 0;                                                                                       \
         if (smem > 48 * 1024 && smem > configured) {                                                                        \
-            const cudaError_t e = cudaFuncSetAttribute(route_kernel<TA, TA, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            const cudaError_t e = cudaFuncSetAttribute(route_kernel<TPB, TA, TA, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
             if (e != cudaSuccess) return (int)e;                                                                            \
             configured = 200 * 1024;                                                                                        \
         }                                                                                                                   \
-        CELLM_RUN((route_kernel<TA, TA, TC>), blocks, ROUTE_THREADS, smem, stream, idx, wts, gate_out, (const TA*)y, ldy,   \
+        CELLM_RUN((route_kernel<TPB, TA, TA, TC>), blocks, ROUTE_THREADS, smem, stream, idx, wts, gate_out, (const TA*)y, ldy, \
                   (const TA*)router, (const TC*)correction, T, H, E, top, n_groups, keep, scale, has_gate);                 \
+    } while (0)
+#define GO(TA, TC)                          \
+    do {                                    \
+        if (tpb == 8) GO2(8, TA, TC);       \
+        else GO2(1, TA, TC);                \
     } while (0)
     if (act_dtype == CELLM_F32 && c_dtype == CELLM_F32) GO(float, float);
     else if (act_dtype == CELLM_F32 && c_dtype == CELLM_BF16) GO(float, __nv_bfloat16);
     else if (act_dtype == CELLM_BF16 && c_dtype == CELLM_F32) GO(__nv_bfloat16, float);
     else if (act_dtype == CELLM_BF16 && c_dtype == CELLM_BF16) GO(__nv_bfloat16, __nv_bfloat16);
     else return CELLM_ERR_DTYPE;
+#undef GO2
 #undef GO
     return CELLM_OK;
 }
@@ -301,5 +299,125 @@ CELLM_API int cellm_activation(void* h, const float* u, long long ld, int T, int
     if (dtype == CELLM_F32) CELLM_RUN(activation_kernel<float>, blocks, 256, 0, stream, (float*)h, u, ld, n, act, total);
     else if (dtype == CELLM_BF16) CELLM_RUN(activation_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)h, u, ld, n, act, total);
     else return CELLM_ERR_DTYPE;
+    return CELLM_OK;
+}
+
+// ---- many tokens: the (token, choice) slots sorted by expert ------------------------------------------------------------
+// For the grouped tensor-core product every expert's slots form one run of rows, padded to whole tiles of 128 rows, in
+// the order of the slots themselves (so a row's place depends on the step's tokens alone, never on timing).
+#define MOE_TILE 128
+#define MOE_SORT_THREADS 256
+
+// One block an expert: it counts the slots of every expert (a histogram in shared memory), finds where its own run
+// begins, names its tiles, and places its slots in their order. row_slot[row] = slot or -1 (padding); slot_row[slot] = row;
+// tile_group[tile] = expert or -1 (behind the last run).
+__global__ void __launch_bounds__(MOE_SORT_THREADS)
+moe_sort_kernel(int* __restrict__ row_slot, int* __restrict__ slot_row, int* __restrict__ tile_group, const int* __restrict__ idx, int S,
+                int E, int max_tiles) {
+    extern __shared__ int sh[];
+    int* hist = sh;             // [E]
+    int* wsum = sh + E;         // [warps]
+    const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = MOE_SORT_THREADS / 32;
+    pdl_trigger();
+    pdl_wait();
+    for (int i = tid; i < E; i += MOE_SORT_THREADS) hist[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < S; i += MOE_SORT_THREADS) {
+        const int x = idx[i];
+        if (x >= 0 && x < E) atomicAdd(&hist[x], 1);
+    }
+    __syncthreads();
+    int start = 0;
+    for (int f = 0; f < e; ++f) start += (hist[f] + MOE_TILE - 1) / MOE_TILE * MOE_TILE;
+    const int count = hist[e], padded = (count + MOE_TILE - 1) / MOE_TILE * MOE_TILE;
+    for (int i = tid; i < padded / MOE_TILE; i += MOE_SORT_THREADS) tile_group[start / MOE_TILE + i] = e;
+    if (e == E - 1)
+        for (int i = (start + padded) / MOE_TILE + tid; i < max_tiles; i += MOE_SORT_THREADS) tile_group[i] = -1;
+    for (int i = count + tid; i < padded; i += MOE_SORT_THREADS) row_slot[start + i] = -1;
+    int base = 0;
+    for (int c0 = 0; c0 < S; c0 += MOE_SORT_THREADS) {
+        const int i = c0 + tid;
+        const bool mine = i < S && idx[i] == e;
+        const unsigned b = __ballot_sync(0xffffffffu, mine);
+        if (lane == 0) wsum[warp] = __popc(b);
+        __syncthreads();
+        int before = 0, total = 0;
+        for (int w = 0; w < nwarps; ++w) {
+            if (w < warp) before += wsum[w];
+            total += wsum[w];
+        }
+        if (mine) {
+            const int r = start + base + before + __popc(b & ((1u << lane) - 1u));
+            row_slot[r] = i;
+            slot_row[i] = r;
+        }
+        base += total;
+        __syncthreads();
+    }
+}
+
+CELLM_API int cellm_moe_sort(int* row_slot, int* slot_row, int* tile_group, const int* idx, int S, int E, int max_tiles, cudaStream_t stream) {
+    if (S <= 0) return CELLM_OK;
+    if (E < 1 || max_tiles < 1 || E > 8192) return CELLM_ERR_SIZE;
+    CELLM_RUN(moe_sort_kernel, E, MOE_SORT_THREADS, (size_t)(E + 32) * sizeof(int), stream, row_slot, slot_row, tile_group, idx, S, E, max_tiles);
+    return CELLM_OK;
+}
+
+// xs[row, :] = y[row_slot[row] / top, :] for the rows of the named tiles (zeros in padding rows); 16-byte pieces.
+__global__ void moe_gather_kernel(uint4* __restrict__ xs, const uint4* __restrict__ y, long long ldy16, const int* __restrict__ row_slot,
+                                  const int* __restrict__ tile_group, int top, int H16) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x;
+    if (tile_group[row / MOE_TILE] < 0) return;
+    const int slot = row_slot[row];
+    uint4* dst = xs + (size_t)row * H16;
+    if (slot < 0) {
+        for (int i = threadIdx.x; i < H16; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+        return;
+    }
+    const uint4* src = y + (size_t)(slot / top) * ldy16;
+    for (int i = threadIdx.x; i < H16; i += blockDim.x) dst[i] = src[i];
+}
+
+// rows: the sorted buffer's rows (a multiple of 128); y: [T, H] bfloat16 with H a multiple of 8.
+CELLM_API int cellm_moe_gather(void* xs, const void* y, long long ldy, const int* row_slot, const int* tile_group, int rows, int top, int H,
+                               cudaStream_t stream) {
+    if (rows <= 0) return CELLM_OK;
+    if ((H & 7) || (ldy & 7) || (rows % MOE_TILE) || top < 1) return CELLM_ERR_SIZE;
+    if (((uintptr_t)xs | (uintptr_t)y) & 15) return CELLM_ERR_ALIGN;
+    CELLM_RUN(moe_gather_kernel, rows, 128, 0, stream, (uint4*)xs, (const uint4*)y, ldy / 8, row_slot, tile_group, top, H / 8);
+    return CELLM_OK;
+}
+
+// out[t, :] = sum_k wts[t, k] * Y[slot_row[t * top + k], :] (+ gate[t] * shared[t, :]), the sum in the order of k, 32-bit.
+__global__ void moe_combine_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ Y, const int* __restrict__ slot_row,
+                                   const float* __restrict__ wts, const float* __restrict__ shared, const float* __restrict__ gate, int H,
+                                   int top) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const float g = shared ? (gate ? gate[t] : 1.f) : 0.f;
+    for (int c = threadIdx.x * 2; c < H; c += blockDim.x * 2) {
+        float a0 = 0.f, a1 = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const float w = wts[(size_t)t * top + k];
+            const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(Y + (size_t)slot_row[(size_t)t * top + k] * H + c));
+            a0 += w * v.x;
+            a1 += w * v.y;
+        }
+        if (shared) {
+            a0 += g * shared[(size_t)t * H + c];
+            a1 += g * shared[(size_t)t * H + c + 1];
+        }
+        *reinterpret_cast<__nv_bfloat162*>(out + (size_t)t * H + c) = __floats2bfloat162_rn(a0, a1);
+    }
+}
+
+CELLM_API int cellm_moe_combine(void* out, const void* Y, const int* slot_row, const float* wts, const float* shared, const float* gate, int T,
+                                int H, int top, cudaStream_t stream) {
+    if (T <= 0) return CELLM_OK;
+    if ((H & 1) || top < 1) return CELLM_ERR_SIZE;
+    CELLM_RUN(moe_combine_kernel, T, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)Y, slot_row, wts, shared, gate, H, top);
     return CELLM_OK;
 }

@@ -1,6 +1,7 @@
 #include "executor.h"
 
 #include <algorithm>
+#include <cstdint>
 #include <stdexcept>
 #include <string>
 
@@ -13,6 +14,7 @@ typedef void* P;
 typedef const void* CP;
 typedef int (*EmbedFn)(P out, CP table, int tag, CP ids, int T, int H, int V, float scale, P err, P stream);
 typedef int (*AddRmsnormFn)(P x, CP delta, CP w, int w_tag, P y, CP rows, int n, int H, int groups, float eps, int act_tag, P stream);
+typedef int (*Add2RmsnormFn)(P x, CP delta, CP delta2, CP w, int w_tag, P y, CP rows, int n, int H, int groups, float eps, int act_tag, P stream);
 typedef int (*ResidualAddFn)(P x, CP delta, i64 n, int act_tag, P stream);
 typedef int (*SwigluFn)(P h, CP gu, int T, int ff, int tag, int gu_tag, P stream);
 typedef int (*ShortConvFn)(P y, CP bcx, CP w, CP bias, int w_tag, P state, i64 slot_stride, CP slot_ids, CP seq, CP cu, int T,
@@ -56,11 +58,16 @@ typedef int (*EmbedPosFn)(P out, CP table, int tag, CP ids, CP pos_table, CP pos
                           P stream);
 typedef int (*AttnPrepFn)(P q, CP qkv, i64 row_stride, CP q_w, CP k_w, int w_tag, float eps, int span, float temp_coef, int temp_every,
                           CP positions, CP seq, CP bt, int bt_stride, P kp, P vp, int num_pages, int page_size, int T, int nh, int nkv,
-                          int hd, int hdv, int act_tag, P err, P stream);
+                          int hd, int hdv, int hq, int hv, int act_tag, P err, P stream);
 typedef int (*RouteFn)(P idx, P wts, P gate, CP y, i64 ldy, CP router, int w_tag, CP correction, int c_tag, int T, int H, int E, int top,
                        int n_groups, int keep, float scale, int has_gate, int act_tag, P stream);
 typedef int (*ExpertsRowwiseFn)(P out, P mid, CP y, i64 ldy, CP up, CP down, CP idx, CP wts, CP shared, CP gate, int T, int H, int ff, int top,
                                 int E, int act, int tag, P stream);
+typedef int (*MoeSortFn)(P row_slot, P slot_row, P tile_group, CP idx, int S, int E, int max_tiles, P stream);
+typedef int (*MoeGatherFn)(P xs, CP y, i64 ldy, CP row_slot, CP tile_group, int rows, int top, int H, P stream);
+typedef int (*MoeCombineFn)(P out, CP Y, CP slot_row, CP wts, CP shared, CP gate, int T, int H, int top, P stream);
+typedef int (*GemmGroupedFn)(P c, CP a, CP w, int M, int N, int K, int groups, i64 lda, i64 ldw, i64 ldc, int out_tag, CP tile_group, int act,
+                             P err, P stream);
 typedef int (*ActivationFn)(P h, CP u, i64 ld, int T, int n, int act, int tag, P stream);
 
 struct KernelError : std::runtime_error {
@@ -213,13 +220,28 @@ struct Run {
     }
 
     // ---- registers -----------------------------------------------------------------------------------------------
-    // a part's output becomes the addend that waits; one that waits already goes into the stream first
+    // A part's output becomes an addend that waits for the next norm. Two may wait at once (a layer whose mixer and
+    // feed-forward read the same norm's output): regs.pending, the older, and pending2. They lie in the two output
+    // slots, so before a third part writes, the older one goes into the stream.
+    const void* pending2 = nullptr;
+    void add_older_now() {
+        if (!regs.pending) return;
+        LAUNCH(fn<ResidualAddFn>(FN_RESIDUAL_ADD)(regs.x, regs.pending, s.T * p.H, (int)act, s.stream), "residual_add");
+        stream_in_y = false;
+        regs.pending = pending2;
+        pending2 = nullptr;
+    }
+    // for what knows one addend only (a Python part, the stream's readers): the second joins the stream at once
+    void one_addend() {
+        if (!pending2) return;
+        LAUNCH(fn<ResidualAddFn>(FN_RESIDUAL_ADD)(regs.x, pending2, s.T * p.H, (int)act, s.stream), "residual_add");
+        stream_in_y = false;
+        pending2 = nullptr;
+    }
     void set_pending(const void* out) {
-        if (regs.pending) {
-            LAUNCH(fn<ResidualAddFn>(FN_RESIDUAL_ADD)(regs.x, regs.pending, s.T * p.H, (int)act, s.stream), "residual_add");
-            stream_in_y = false;
-        }
-        regs.pending = out;
+        if (!regs.pending) regs.pending = out;
+        else if (!pending2) pending2 = out;
+        else throw std::runtime_error("executor: three addends wait");
     }
     const void* input() const {
         if (!regs.y) throw std::runtime_error("executor: a part wants activations before any norm has left some");
@@ -241,10 +263,15 @@ struct Run {
         arena.release();
         const i64 count = rows ? s.R : s.T;
         void* y = arena.take(count * p.H * elt(act));
+        if (pending2)
+            LAUNCH(fn<Add2RmsnormFn>(FN_ADD2_RMSNORM)(regs.x, regs.pending, pending2, n.w, (int)n.dtype, y, rows ? s.rows : nullptr, (int)count,
+                                                  (int)p.H, (int)std::max<i64>(n.groups, 1), (float)n.eps, (int)act, s.stream),
+                   "add2_rmsnorm");
+        else
         LAUNCH(fn<AddRmsnormFn>(FN_ADD_RMSNORM)(regs.x, regs.pending, n.w, (int)n.dtype, y, rows ? s.rows : nullptr, (int)count, (int)p.H,
                                             (int)std::max<i64>(n.groups, 1), (float)n.eps, (int)act, s.stream),
            "add_rmsnorm");
-        if (!rows) regs.pending = nullptr;      // with rows given the stream itself is not touched
+        if (!rows) regs.pending = pending2 = nullptr;      // with rows given the stream itself is not touched
         regs.y = y;
         stream_in_y = false;
     }
@@ -256,12 +283,14 @@ struct Run {
     void python(const PythonParams& py) {
         if (dry) return;
         if (!p.python) throw std::runtime_error("executor: a Python part in a program without a callback");
+        one_addend();
         stream_in_y = false;
         if (p.python(py.token, &regs) != 0) throw std::runtime_error("executor: a Python part raised");
     }
 
     // y = the stream in the activations' type (the 32-bit stream itself when the activations are 32-bit)
     void read_stream() {
+        one_addend();
         if (stream_in_y) return;
         if (regs.pending) {
             LAUNCH(fn<ResidualAddFn>(FN_RESIDUAL_ADD)(regs.x, regs.pending, s.T * p.H, (int)act, s.stream), "residual_add");
@@ -285,6 +314,7 @@ struct Run {
     void gated_norm_add(const GatedNormAddParams& n) {
         if (!regs.pending) throw std::runtime_error("executor: a gate and norm without a sublayer's result before them");
         if (regs.phase != 1) throw std::runtime_error("executor: a gate and norm outside the layers");
+        if (pending2) throw std::runtime_error("executor: a gate and norm with two results before them");
         const i64 T = s.T, H = p.H;
         const void* g = nullptr;
         i64 g_ld = H, g_dtype = act;
@@ -363,6 +393,7 @@ struct Run {
             case OP_READ_STREAM: read_stream(); break;
             case OP_GATED_NORM_ADD: gated_norm_add(*static_cast<const GatedNormAddParams*>(op.params)); break;
             case OP_SHORT_CONV: case OP_ATTENTION: case OP_SWIGLU: case OP_MINGRU: case OP_LATENT_ATTENTION: case OP_GATED_MLP: case OP_ROUTED_MLP: {
+                if (regs.pending && pending2) add_older_now();      // both output slots are taken: the older addend's is written next
                 void* out = slot[turn];
                 produce(op, it, input(), out);
                 set_pending(out);
@@ -601,19 +632,28 @@ void Run::attention(const AttentionParams& L, const ExecItem& it, const void* x,
     const i64 nkv = it.writes ? L.nkv : 0;
     void* q = nullptr;
     const i64 hdv = L.hdv > 0 ? L.hdv : hd;
-    if (hdv != hd || L.norm_whole || L.temp_coef != 0.0) {
+    if (hdv != hd || L.norm_whole || L.temp_coef != 0.0 || L.pad) {
         // the general form: values of a width of their own, a norm over the whole projection, a query temperature
         if (L.rot || L.inv_freq) throw std::runtime_error("executor: the general attention form has no rotation");
-        const i64 width = nh * hd + nkv * (hd + hdv);
+        if (L.pad && (L.pad < hd || L.pad < hdv)) throw std::runtime_error("executor: heads padded to less than their width");
+        const i64 width = nh * hd + nkv * (hd + hdv), hq = L.pad ? L.pad : hd, hv = L.pad ? L.pad : hdv;
         void* qkv = linear(x, L.qkv, T, H, act, width);       // without a cache of its own: the query rows only
-        q = arena.take(T * nh * hd * elt(act));
+        q = arena.take(T * nh * hq * elt(act));
         const int span = L.q_norm_w ? (L.norm_whole ? 2 : 1) : 0;
         LAUNCH(fn<AttnPrepFn>(FN_ATTN_PREP)(q, qkv, width, L.q_norm_w, L.k_norm_w, L.q_norm_w ? (int)L.qk_dtype : 0, (float)L.qk_eps, span,
                                         (float)L.temp_coef, (int)L.temp_every, s.positions, s.seq_of_token,
                                         nkv ? it.block_table : nullptr, nkv ? (int)it.bt_stride : 0, nkv ? it.k : nullptr,
                                         nkv ? it.v : nullptr, nkv ? (int)it.num_pages : 0, (int)it.page_size, (int)T, (int)nh, (int)nkv,
-                                        (int)hd, (int)hdv, (int)act, s.err, s.stream),
+                                        (int)hd, (int)hdv, (int)hq, (int)hv, (int)act, s.err, s.stream),
                "attn_prep");
+        if (L.pad) {        // from here on an ordinary attention with heads of the padded width
+            AttentionParams P = L;
+            P.hd = L.pad;
+            P.hdv = 0;
+            void* o = attend(P, it, q);
+            product(out, o, L.out_proj, T, nh * L.pad, act);
+            return;
+        }
         void* o = attend(L, it, q);
         product(out, o, L.out_proj, T, nh * hdv, act);
         return;
@@ -683,6 +723,27 @@ void Run::routed_mlp(const RoutedMlpParams& L, const void* x, void* out) {
         void* h = arena.take(T * L.shared_ff * e);
         LAUNCH(fn<ActivationFn>(FN_ACTIVATION)(h, u, L.shared_ff, (int)T, (int)L.shared_ff, (int)L.act, (int)act, s.stream), "activation");
         shared = linear(h, L.shared_down, T, L.shared_ff, EXEC_F32);
+    }
+    if (act == EXEC_BF16 && T >= p.grouped_min_tokens && tc_ok(L.up, H) && tc_ok(L.down, L.ff) && (((uintptr_t)x) & 15) == 0) {
+        // many tokens: the slots sorted by expert, every expert's run padded to whole tiles of 128 rows, and the two
+        // products as grouped tensor-core products over the sorted rows (the activation in the first one's epilogue)
+        const i64 S = T * L.top, rows = ceil_div(S + std::min(L.experts, S) * 127, 128) * 128, tiles = rows / 128;
+        void* row_slot = arena.take(rows * 4);
+        void* slot_row = arena.take(S * 4);
+        void* tile_group = arena.take(tiles * 4);
+        LAUNCH(fn<MoeSortFn>(FN_MOE_SORT)(row_slot, slot_row, tile_group, idx, (int)S, (int)L.experts, (int)tiles, s.stream), "moe_sort");
+        void* xs = arena.take(rows * H * 2);
+        LAUNCH(fn<MoeGatherFn>(FN_MOE_GATHER)(xs, x, H, row_slot, tile_group, (int)rows, (int)L.top, (int)H, s.stream), "moe_gather");
+        void* mid = arena.take(rows * L.ff * 2);
+        LAUNCH(fn<GemmGroupedFn>(FN_GEMM_GROUPED)(mid, xs, L.up.w, (int)rows, (int)L.ff, (int)H, (int)L.experts, H, L.up.ldw, L.ff, (int)EXEC_BF16,
+                                              tile_group, (int)L.act, s.err, s.stream),
+               "gemm_grouped_tcgen05");
+        void* ys = arena.take(rows * H * 2);
+        LAUNCH(fn<GemmGroupedFn>(FN_GEMM_GROUPED)(ys, mid, L.down.w, (int)rows, (int)H, (int)L.ff, (int)L.experts, L.ff, L.down.ldw, H,
+                                              (int)EXEC_BF16, tile_group, -1, s.err, s.stream),
+               "gemm_grouped_tcgen05");
+        LAUNCH(fn<MoeCombineFn>(FN_MOE_COMBINE)(out, ys, slot_row, wts, shared, gate, (int)T, (int)H, (int)L.top, s.stream), "moe_combine");
+        return;
     }
     void* mid = arena.take(T * L.top * L.ff * e);
     LAUNCH(fn<ExpertsRowwiseFn>(FN_EXPERTS_ROWWISE)(out, mid, x, H, L.up.w, L.down.w, idx, wts, shared, gate, (int)T, (int)H, (int)L.ff,

@@ -79,6 +79,8 @@ struct AttentionParams {
     i64 hdv;                // width of a value head (0: hd); the item's pool of values has rows of this width
     i64 norm_whole;         // 1: q and k are normed over all their heads at once (weights [nh * hd], [nkv * hd]); 0: per head
     double temp_coef; i64 temp_every;       // q *= 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1); coef 0: none
+    i64 pad;                // > 0: queries, keys and values are kept in heads of this width, zeros behind their own entries, so that
+                            // the attention is an ordinary one of that head size; out_proj then has nh * pad columns
 };
 struct SwiGLUParams {
     ExecLinear gate_up, down;
@@ -146,7 +148,8 @@ enum ExecFn {
     FN_EMBED, FN_ADD_RMSNORM, FN_RESIDUAL_ADD, FN_SWIGLU, FN_SHORT_CONV, FN_QK_NORM_ROPE, FN_ATTENTION_PLAIN, FN_GEMM_PLAIN,
     FN_ATTENTION_DECODE, FN_ATTENTION_TC, FN_ATTENTION_FLASH, FN_GEMM_TCGEN05, FN_GEMM_CONV, FN_GEMM_ROPE,
     FN_GATED_NORM_ADD, FN_STREAM_CAST, FN_MINGRU_SCAN, FN_LATENT_PREP, FN_HEAD_PRODUCT, FN_GATED_ACT, FN_BIAS_ADD, FN_ATTENTION_LATENT, FN_HEAD_PRODUCT_MMA,
-    FN_EMBED_POS, FN_ATTN_PREP, FN_ATTENTION_PLAIN_WIDE, FN_ROUTE, FN_EXPERTS_ROWWISE, FN_ACTIVATION, FN_COUNT
+    FN_EMBED_POS, FN_ATTN_PREP, FN_ATTENTION_PLAIN_WIDE, FN_ROUTE, FN_EXPERTS_ROWWISE, FN_ACTIVATION, FN_ADD2_RMSNORM,
+    FN_MOE_SORT, FN_MOE_GATHER, FN_MOE_COMBINE, FN_GEMM_GROUPED, FN_COUNT
 };
 
 struct ExecProgram {
@@ -154,6 +157,7 @@ struct ExecProgram {
     i64 sms, static_flag, max_counters;
     i64 fused_conv, fused_rope;     // decode steps: in_proj + convolution, q/k/v product + norm + rotation as one kernel each
     i64 latent_tc;                  // latent attention on the tensor cores where its sizes allow (0: the plain kernel always)
+    i64 grouped_min_tokens;         // routed experts run as grouped tensor-core products from this many tokens (bfloat16)
     i64 tc_min_ctas;                // prompt attention on tcgen05 from this many CTAs (< 0: an eighth of the SMs)
     double tc_min_fill;             // and this share of its tiles' rows in use
     ExecOps prologue, epilogue;

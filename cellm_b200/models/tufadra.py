@@ -32,7 +32,7 @@ def build_plan(cfg: TufadraConfig) -> ModelPlan:
         mixer = PartSpec(
             "attention",
             {"hidden_size": H, "num_heads": m.heads, "num_kv_heads": m.kv_heads, "head_dim": m.dim, "value_dim": m.vdim,
-             "scale": m.scale, "window": 0, "position": None,
+             "scale": m.scale, "window": 0, "position": None, "pad_heads": True,
              "qk_norm": PartSpec("rms_norm", {"dim": m.dim, "eps": cfg.norm_eps}), "qk_norm_span": "projection",
              "query_temperature": {"coef": m.q_temp.coef, "every": m.q_temp.every} if m.q_temp is not None else None},
             {"q_proj": p + "mix.q", "k_proj": p + "mix.k", "v_proj": p + "mix.v", "out_proj": p + "mix.o",

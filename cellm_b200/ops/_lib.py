@@ -22,6 +22,7 @@ _SIGNATURES = {
         "cellm_embed_pos": [P, P, I, P, P, P, I, I, I, I, F, P, P],
         "cellm_upload": [P, P, L, P],
         "cellm_add_rmsnorm": [P, P, P, I, P, P, I, I, I, F, I, P],
+        "cellm_add2_rmsnorm": [P, P, P, P, I, P, P, I, I, I, F, I, P],
         "cellm_residual_add": [P, P, L, I, P],
         "cellm_swiglu": [P, P, I, I, I, I, P],
         "cellm_short_conv": [P, P, P, P, I, P, L, P, P, P, I, I, I, I, I, I, I, P, P],
@@ -34,11 +35,14 @@ _SIGNATURES = {
         "cellm_head_product": [P, L, L, P, L, L, P, I, I, I, I, I, P],
         "cellm_gated_act": [P, P, L, P, P, I, I, I, I, I, I, P],
         "cellm_bias_add": [P, P, P, I, I, I, I, P],
-        "cellm_attn_prep": [P, P, L, P, P, I, F, I, F, I, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, P],
+        "cellm_attn_prep": [P, P, L, P, P, I, F, I, F, I, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, I, P, P],
         "cellm_attention_plain_wide": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P],
         "cellm_route": [P, P, P, P, L, P, I, P, I, I, I, I, I, I, I, F, I, I, P],
         "cellm_experts_rowwise": [P, P, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
         "cellm_activation": [P, P, L, I, I, I, I, P],
+        "cellm_moe_sort": [P, P, P, P, I, I, I, P],
+        "cellm_moe_gather": [P, P, L, P, P, I, I, I, P],
+        "cellm_moe_combine": [P, P, P, P, P, P, I, I, I, P],
         "cellm_argmax": [P, P, I, I, P, P],
         "cellm_take_pending_tokens": [P, P, P, P, I, I, P, P],
         "cellm_keep_last_tokens": [P, P, P, I, I, P],
@@ -65,6 +69,7 @@ _SIGNATURES = {
     },
     "gemm_tcgen05": {
         "cellm_gemm_tcgen05": [P, P, P, I, I, I, L, L, L, I, I, I, I, I, P, P, P, P],
+        "cellm_gemm_grouped_tcgen05": [P, P, P, I, I, I, I, L, L, L, I, P, I, P, P],
         "cellm_gemm_conv_tcgen05": [P, P, P, I, I, I, L, L, I, I, I, P, P, I, P, L, P, I, I, P, P],
         "cellm_gemm_rope_tcgen05": [P, P, P, I, I, L, L, I, I, P, P, F, P, P, I, P, P, I, I, I, I, P, I, P, P],
     },

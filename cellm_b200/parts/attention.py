@@ -5,7 +5,11 @@ pages, softmax(q.k * scale) over all earlier keys (or a window), out_proj.
 
 Beyond the reference's form, as parameters: values of a width of their own (`value_dim`), the norm of q and k
 taken over the whole projection instead of per head (`qk_norm_span`: "projection"), and a query temperature
-that grows with the position, q *= 1 + coef * ln(floor((pos + 1) / every) + 1) (`query_temperature`)."""
+that grows with the position, q *= 1 + coef * ln(floor((pos + 1) / every) + 1) (`query_temperature`). With
+`pad_heads`, heads whose key and value widths differ, or are none of the widths the fast attention kernels take, are
+kept (queries, cached keys and values) in heads of the next such width with zeros behind their own entries: the scores
+are the same sums, the values' last columns are zero, and out_proj gets zero columns to match."""
+
 from __future__ import annotations
 
 import torch
@@ -16,6 +20,17 @@ from .base import CacheBinding, Mixer, PagedKV, StepContext, TensorSpec
 from .linear import Linear, stack_rows
 from .registry import part_class, register_mixer
 
+FAST_HEAD_WIDTHS = (32, 64, 128)
+
+
+def padded_head_width(params: dict) -> int:
+    """The width heads are kept in when `pad_heads` is set and it helps (0: as they are)."""
+    hd = int(params["head_dim"])
+    vd = int(params.get("value_dim") or hd)
+    if not params.get("pad_heads") or (hd == vd and hd in FAST_HEAD_WIDTHS) or max(hd, vd) > FAST_HEAD_WIDTHS[-1]:
+        return 0
+    return next(w for w in FAST_HEAD_WIDTHS if w >= max(hd, vd))
+
 
 class AttentionMixer(Mixer):
     graph_safe = True
@@ -23,7 +38,7 @@ class AttentionMixer(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, scale, window,
     qk_norm (PartSpec of a norm over head_dim, or None), position (PartSpec or None),
     value_dim (default head_dim), qk_norm_span ("head", the default, or "projection"),
-    query_temperature ({"coef", "every"} or None).
+    query_temperature ({"coef", "every"} or None), pad_heads (default False).
     weights: q_proj [nh*hd, H], k_proj [nkv*hd, H], v_proj [nkv*vd, H], out_proj [H, nh*vd],
     q_norm, k_norm [hd] if qk_norm ([nh*hd] and [nkv*hd] when its span is the projection)."""
 
@@ -44,6 +59,8 @@ class AttentionMixer(Mixer):
     @classmethod
     def cache_need(cls, params):
         hd, vd = int(params["head_dim"]), int(params.get("value_dim") or params["head_dim"])
+        if padded_head_width(params):
+            return PagedKV(int(params["num_kv_heads"]), padded_head_width(params), int(params.get("window", 0)))
         return PagedKV(int(params["num_kv_heads"]), hd, int(params.get("window", 0)), value_dim=vd if vd != hd else 0)
 
     def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
@@ -63,7 +80,8 @@ class AttentionMixer(Mixer):
         if self.temp_every < 1:
             raise ConfigError(f"attention: query_temperature.every must be positive, not {self.temp_every}")
         # what only the general kernels take (no rotation there)
-        self.general = self.vd != self.hd or self.norm_whole or self.temp_coef != 0.0
+        self.pad = padded_head_width(params)
+        self.general = self.vd != self.hd or self.norm_whole or self.temp_coef != 0.0 or self.pad > 0
         if self.general and params.get("position") is not None:
             raise ConfigError("attention: a position encoding together with value_dim, a norm over the projection or a "
                               "query temperature is not built")
@@ -71,7 +89,12 @@ class AttentionMixer(Mixer):
         dev = weights["q_proj"].device
         self.qkv = Linear(stack_rows(weights["q_proj"], weights["k_proj"], weights["v_proj"]), dtype)
         self.q_only = Linear(self.qkv.weight[:self.nh * self.hd], dtype)   # rows of the stacked matrix, no copy
-        self.out_proj = Linear(weights["out_proj"], dtype)
+        out_w = weights["out_proj"]
+        if self.pad:        # zero columns where the padded heads' values are zero
+            wide = torch.zeros((self.H, self.nh, self.pad), dtype=out_w.dtype, device=out_w.device)
+            wide[:, :, :self.vd] = out_w.reshape(self.H, self.nh, self.vd)
+            out_w = wide.reshape(self.H, self.nh * self.pad)
+        self.out_proj = Linear(out_w, dtype)
         qk: PartSpec | None = params.get("qk_norm")
         self.q_norm_w = self.k_norm_w = None
         self.norm_eps = 0.0
@@ -107,7 +130,7 @@ class AttentionMixer(Mixer):
         p = R.AttentionParams()
         p.nh, p.nkv, p.hd, p.window, p.scale = self.nh, self.nkv, self.hd, self.window, self.scale
         p.hdv = self.vd if self.vd != self.hd else 0
-        p.norm_whole, p.temp_coef, p.temp_every = int(self.norm_whole), self.temp_coef, self.temp_every
+        p.norm_whole, p.temp_coef, p.temp_every, p.pad = int(self.norm_whole), self.temp_coef, self.temp_every, self.pad
         return p
 
     def emit(self, emitter) -> None:

@@ -29,7 +29,10 @@ from . import records as R
 # and the q/k/v product + head norms + rotation + cache write, as one kernel each. attention_tc_*: prompt attention
 # goes to the tcgen05 kernel from this many CTAs (None: an eighth of the SMs) and this share of its tiles' rows in use.
 # latent_tc: latent attention runs on the tensor cores where its sizes allow (off: the plain kernel, as in 32-bit).
-OPTIONS = {"fused_conv": True, "fused_rope": True, "attention_tc_min_ctas": None, "attention_tc_min_fill": 0.5, "latent_tc": True}
+# grouped_experts_min_tokens: routed experts run as grouped tensor-core products from this many tokens of a step (fewer
+# tokens walk their experts row by row).
+OPTIONS = {"fused_conv": True, "fused_rope": True, "attention_tc_min_ctas": None, "attention_tc_min_fill": 0.5, "latent_tc": True,
+           "grouped_experts_min_tokens": 17}
 
 _bound = False
 
@@ -178,6 +181,7 @@ class Program:
         p = self.program
         p.fused_conv, p.fused_rope = int(OPTIONS["fused_conv"]), int(OPTIONS["fused_rope"])
         p.latent_tc = int(OPTIONS["latent_tc"])
+        p.grouped_min_tokens = int(OPTIONS["grouped_experts_min_tokens"])
         p.tc_min_ctas = -1 if OPTIONS["attention_tc_min_ctas"] is None else int(OPTIONS["attention_tc_min_ctas"])
         p.tc_min_fill = float(OPTIONS["attention_tc_min_fill"])
 

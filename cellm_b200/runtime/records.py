@@ -48,7 +48,7 @@ class AttentionParams(Structure):
     _fields_ = [("qkv", ExecLinear), ("out_proj", ExecLinear), ("nh", I64), ("nkv", I64), ("hd", I64), ("window", I64),
                 ("scale", F64), ("q_norm_w", PTR), ("k_norm_w", PTR), ("qk_dtype", I64), ("qk_eps", F64),
                 ("rot", I64), ("interleaved", I64), ("inv_freq", PTR), ("hdv", I64), ("norm_whole", I64),
-                ("temp_coef", F64), ("temp_every", I64)]
+                ("temp_coef", F64), ("temp_every", I64), ("pad", I64)]
 
 
 class SwiGLUParams(Structure):
@@ -119,7 +119,9 @@ ENTRY_POINTS = [("kernels_common", "cellm_embed"), ("kernels_common", "cellm_add
                 ("attention_latent", "cellm_attention_latent"), ("attention_latent", "cellm_head_product_mma"),
                 ("kernels_common", "cellm_embed_pos"), ("kernels_common", "cellm_attn_prep"),
                 ("kernels_common", "cellm_attention_plain_wide"), ("kernels_common", "cellm_route"),
-                ("kernels_common", "cellm_experts_rowwise"), ("kernels_common", "cellm_activation")]
+                ("kernels_common", "cellm_experts_rowwise"), ("kernels_common", "cellm_activation"),
+                ("kernels_common", "cellm_add2_rmsnorm"), ("kernels_common", "cellm_moe_sort"), ("kernels_common", "cellm_moe_gather"),
+                ("kernels_common", "cellm_moe_combine"), ("gemm_tcgen05", "cellm_gemm_grouped_tcgen05")]
 # libraries a model whose activations are 32-bit never calls into (they need not be compiled for it)
 BF16_ONLY_LIBRARIES = ("attention_decode", "attention_tc", "attention_flash", "gemm_tcgen05", "attention_latent")
 # libraries that only records of these kinds reach (a program without such a record need not have them compiled)
@@ -130,7 +132,7 @@ LIBRARY_USERS = {"attention_decode": (ATTENTION, ATTEND), "attention_tc": (ATTEN
 class ExecProgram(Structure):
     _fields_ = [("n_layers", I64), ("n_order", I64), ("H", I64), ("V", I64), ("act_dtype", I64),
                 ("sms", I64), ("static_flag", I64), ("max_counters", I64), ("fused_conv", I64), ("fused_rope", I64),
-                ("latent_tc", I64), ("tc_min_ctas", I64), ("tc_min_fill", F64),
+                ("latent_tc", I64), ("grouped_min_tokens", I64), ("tc_min_ctas", I64), ("tc_min_fill", F64),
                 ("prologue", ExecOps), ("epilogue", ExecOps), ("layers", POINTER(ExecOps)), ("order", POINTER(I64)),
                 ("python", PythonOpFn), ("fns", PTR * len(ENTRY_POINTS))]
 
