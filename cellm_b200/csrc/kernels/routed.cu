@@ -12,7 +12,7 @@
 // that depends on the sizes alone, so a token's result does not depend on what else is in the batch.
 #include "common.cuh"
 
-#define ROUTE_THREADS 128
+#define ROUTE_THREADS 512
 
 // A lane's share of the dot product of a weight row with a vector held as floats: pieces of 16 bytes where the
 // row allows it (`vec`), else element by element.
@@ -22,9 +22,11 @@ template <>
 __device__ __forceinline__ float lane_dot<float>(const float* __restrict__ w, const float* __restrict__ v, int n, int lane, bool vec) {
     float a = 0.f;
     if (vec) {
+#pragma unroll 4
         for (int i = lane * 4; i < n; i += 128) {
             const float4 x = *reinterpret_cast<const float4*>(w + i);
-            a += x.x * v[i] + x.y * v[i + 1] + x.z * v[i + 2] + x.w * v[i + 3];
+            const float4 y = *reinterpret_cast<const float4*>(v + i);
+            a += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
         }
     } else {
         for (int i = lane; i < n; i += 32) a += w[i] * v[i];
@@ -36,14 +38,13 @@ __device__ __forceinline__ float lane_dot<__nv_bfloat16>(const __nv_bfloat16* __
                                                         bool vec) {
     float a = 0.f;
     if (vec) {
+#pragma unroll 4
         for (int i = lane * 8; i < n; i += 256) {
             const uint4 x = *reinterpret_cast<const uint4*>(w + i);
+            const float4 y0 = *reinterpret_cast<const float4*>(v + i), y1 = *reinterpret_cast<const float4*>(v + i + 4);
             const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&x);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 f = __bfloat1622float2(p[j]);
-                a += f.x * v[i + 2 * j] + f.y * v[i + 2 * j + 1];
-            }
+            const float2 f0 = __bfloat1622float2(p[0]), f1 = __bfloat1622float2(p[1]), f2 = __bfloat1622float2(p[2]), f3 = __bfloat1622float2(p[3]);
+            a += f0.x * y0.x + f0.y * y0.y + f1.x * y0.z + f1.y * y0.w + f2.x * y1.x + f2.y * y1.y + f3.x * y1.z + f3.y * y1.w;
         }
     } else {
         for (int i = lane; i < n; i += 32) a += __bfloat162float(w[i]) * v[i];
@@ -63,7 +64,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS)
 route_kernel(int* __restrict__ idx, float* __restrict__ wts, float* __restrict__ gate_out, const TA* __restrict__ y, long long ldy,
              const TW* __restrict__ router, const TC* __restrict__ correction, int T, int H, int E, int top, int n_groups, int keep,
              float scale, int has_gate) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     float* hs = smem;                               // [TPB][H]
     float* sc = hs + (size_t)ROUTE_TPB * H;         // [TPB][E + 1]: logits, then s
     float* ch = sc + ROUTE_TPB * (E + 1);           // [TPB][E]: choice scores
@@ -80,15 +81,37 @@ route_kernel(int* __restrict__ idx, float* __restrict__ wts, float* __restrict__
     }
     __syncthreads();
     const int rows = E + (has_gate ? 1 : 0);
+    const bool vec = rows_vectorise(router, H, H);
+    constexpr int PER = 16 / (int)sizeof(TW);       // elements in a 16-byte piece of a router row
     for (int r = warp; r < rows; r += nwarps) {
         float acc[ROUTE_TPB];
 #pragma unroll
         for (int j = 0; j < ROUTE_TPB; ++j) acc[j] = 0.f;
         const TW* wr = router + (size_t)r * H;
-        for (int i = lane; i < H; i += 32) {
-            const float w = to_float(wr[i]);
+        if (vec) {
+            for (int i = lane * PER; i < H; i += 32 * PER) {
+                float w[PER];
+                const uint4 x = *reinterpret_cast<const uint4*>(wr + i);
+                const TW* xp = reinterpret_cast<const TW*>(&x);
 #pragma unroll
-            for (int j = 0; j < ROUTE_TPB; ++j) acc[j] += w * hs[j * H + i];
+                for (int k = 0; k < PER; ++k) w[k] = to_float(xp[k]);
+#pragma unroll
+                for (int j = 0; j < ROUTE_TPB; ++j) {
+                    if (j < nt) {
+#pragma unroll
+                        for (int k = 0; k < PER; k += 4) {
+                            const float4 y = *reinterpret_cast<const float4*>(hs + j * H + i + k);
+                            acc[j] += w[k] * y.x + w[k + 1] * y.y + w[k + 2] * y.z + w[k + 3] * y.w;
+                        }
+                    }
+                }
+            }
+        } else {
+            for (int i = lane; i < H; i += 32) {
+                const float w = to_float(wr[i]);
+#pragma unroll
+                for (int j = 0; j < ROUTE_TPB; ++j) acc[j] += w * hs[j * H + i];
+            }
         }
 #pragma unroll
         for (int j = 0; j < ROUTE_TPB; ++j) {
@@ -192,74 +215,85 @@ CELLM_API int cellm_route(int* idx, float* wts, float* gate_out, const void* y, 
 
 // ---- the experts, row by row ----------------------------------------------------------------------------------------
 #define EXPERT_THREADS 128
-#define EXPERT_ROWS 32          // output rows a block forms
+#define EXPERT_ROWS 4           // output rows a block forms: one a warp
 
-// mid[t * top + k, :] = act(U_e y[t]) for e = idx[t, k]; up: [E * ff, H]
+// mid[t * top + k, :] = act(U_e y[t]) for e = idx[t, k]; up: [E * ff, H]. Blocks with blockIdx.x >= T * top take the shared
+// expert: smid[t, :] = act(U_s y[t]), U_s: [sff, H].
 template <typename TA>
 __global__ void __launch_bounds__(EXPERT_THREADS)
-expert_up_kernel(TA* __restrict__ mid, const TA* __restrict__ y, long long ldy, const TA* __restrict__ up, const int* __restrict__ idx,
-                 int H, int ff, int top, int E, int act) {
-    extern __shared__ float smem[];
+expert_up_kernel(TA* __restrict__ mid, TA* __restrict__ smid, const TA* __restrict__ y, long long ldy, const TA* __restrict__ up,
+                 const TA* __restrict__ sup, const int* __restrict__ idx, int T, int H, int ff, int sff, int top, int E, int act) {
+    extern __shared__ __align__(16) float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int slot = blockIdx.x, t = slot / top;
-    const bool vec = rows_vectorise(up, H, H);
+    const bool is_shared = (int)blockIdx.x >= T * top;
+    const int slot = is_shared ? (int)blockIdx.x - T * top : (int)blockIdx.x;
+    const int t = is_shared ? slot : slot / top;
+    const int rows = is_shared ? sff : ff;
+    if ((int)blockIdx.y * EXPERT_ROWS >= rows) return;
+    const bool vec = rows_vectorise(is_shared ? sup : up, H, H);
     pdl_trigger();
     pdl_wait();
     for (int i = threadIdx.x; i < H; i += EXPERT_THREADS) smem[i] = to_float(y[(size_t)t * ldy + i]);
-    int e = idx[slot];
-    e = min(max(e, 0), E - 1);
+    const TA* base = sup;
+    if (!is_shared) base = up + (size_t)min(max(idx[slot], 0), E - 1) * ff * H;
     __syncthreads();
-    const int r_end = min(ff, (int)(blockIdx.y + 1) * EXPERT_ROWS);
-    for (int r = blockIdx.y * EXPERT_ROWS + warp; r < r_end; r += EXPERT_THREADS / 32) {
-        const float d = warp_sum(lane_dot<TA>(up + ((size_t)e * ff + r) * H, smem, H, lane, vec));
-        if (lane == 0) mid[(size_t)slot * ff + r] = from_float<TA>(cellm_activate(d, act));
+    const int r = blockIdx.y * EXPERT_ROWS + warp;
+    if (r < rows) {
+        const float d = warp_sum(lane_dot<TA>(base + (size_t)r * H, smem, H, lane, vec));
+        if (lane == 0) (is_shared ? smid : mid)[(size_t)slot * rows + r] = from_float<TA>(cellm_activate(d, act));
     }
 }
 
-// out[t, r] = sum_k wts[t, k] * (D_e mid[t * top + k])[r] (+ gate[t] * shared[t, r]); down: [E * H, ff]
+// out[t, r] = sum_k wts[t, k] * (D_e mid[t * top + k])[r] (+ gate[t] * (D_s smid[t])[r]); down: [E * H, ff], D_s: [H, sff]
 template <typename TA>
 __global__ void __launch_bounds__(EXPERT_THREADS)
-expert_down_kernel(TA* __restrict__ out, const TA* __restrict__ mid, const TA* __restrict__ down, const int* __restrict__ idx,
-                   const float* __restrict__ wts, const float* __restrict__ shared, const float* __restrict__ gate, int H, int ff, int top,
-                   int E) {
-    extern __shared__ float smem[];             // [top * ff] the token's middles, then [top] weights and experts
+expert_down_kernel(TA* __restrict__ out, const TA* __restrict__ mid, const TA* __restrict__ smid, const TA* __restrict__ down,
+                   const TA* __restrict__ sdown, const int* __restrict__ idx, const float* __restrict__ wts, const float* __restrict__ gate,
+                   int H, int ff, int sff, int top, int E) {
+    extern __shared__ __align__(16) float smem[];   // [top * ff] the token's middles, [sff] the shared expert's, then [top] weights and experts
     float* ms = smem;
-    float* wk = smem + (size_t)top * ff;
+    float* ss = smem + (size_t)top * ff;
+    float* wk = ss + sff;
     int* ek = (int*)(wk + top);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
-    const bool vec = rows_vectorise(down, ff, ff);
+    const bool vec = rows_vectorise(down, ff, ff) && (ff & 3) == 0, svec = sdown && rows_vectorise(sdown, sff, sff) && ((top * ff) & 3) == 0;
     pdl_trigger();
     pdl_wait();
     for (int i = threadIdx.x; i < top * ff; i += EXPERT_THREADS) ms[i] = to_float(mid[(size_t)t * top * ff + i]);
+    if (sdown)
+        for (int i = threadIdx.x; i < sff; i += EXPERT_THREADS) ss[i] = to_float(smid[(size_t)t * sff + i]);
     for (int k = threadIdx.x; k < top; k += EXPERT_THREADS) {
         wk[k] = wts[(size_t)t * top + k];
         ek[k] = min(max(idx[(size_t)t * top + k], 0), E - 1);
     }
     __syncthreads();
-    const int r_end = min(H, (int)(blockIdx.y + 1) * EXPERT_ROWS);
-    for (int r = blockIdx.y * EXPERT_ROWS + warp; r < r_end; r += EXPERT_THREADS / 32) {
+    const int r = blockIdx.y * EXPERT_ROWS + warp;
+    if (r < H) {
         float a = 0.f;
+#pragma unroll 2
         for (int k = 0; k < top; ++k) a += wk[k] * lane_dot<TA>(down + ((size_t)ek[k] * H + r) * ff, ms + (size_t)k * ff, ff, lane, vec);
+        if (sdown) a += (gate ? gate[t] : 1.f) * lane_dot<TA>(sdown + (size_t)r * sff, ss, sff, lane, svec);
         a = warp_sum(a);
-        if (lane == 0) {
-            if (shared) a += (gate ? gate[t] : 1.f) * shared[(size_t)t * H + r];
-            out[(size_t)t * H + r] = from_float<TA>(a);
-        }
+        if (lane == 0) out[(size_t)t * H + r] = from_float<TA>(a);
     }
 }
 
-// The chosen experts of every token, walked row by row. mid: [T * top, ff] scratch of the activations' type.
-// shared: [T, H] float, the shared expert's result before its gate (null: none); gate: [T] (null: the result as it is).
-CELLM_API int cellm_experts_rowwise(void* out, void* mid, const void* y, long long ldy, const void* up, const void* down, const int* idx,
-                                    const float* wts, const float* shared, const float* gate, int T, int H, int ff, int top, int E, int act,
-                                    int dtype, cudaStream_t stream) {
+// The chosen experts of every token, and the shared expert (sup null: none), walked row by row. mid: [T * top, ff] and
+// smid: [T, sff], scratch of the activations' type. gate: [T] (null: the shared expert's result as it is).
+CELLM_API int cellm_experts_rowwise(void* out, void* mid, void* smid, const void* y, long long ldy, const void* up, const void* down,
+                                    const void* sup, const void* sdown, const int* idx, const float* wts, const float* gate, int T, int H,
+                                    int ff, int sff, int top, int E, int act, int dtype, cudaStream_t stream) {
     if (T <= 0) return CELLM_OK;
-    if (H < 1 || ff < 1 || top < 1 || E < 1) return CELLM_ERR_SIZE;
-    const size_t smem_up = (size_t)H * sizeof(float), smem_down = ((size_t)top * ff + 2 * top) * sizeof(float);
+    if (H < 1 || ff < 1 || top < 1 || E < 1 || sff < 0) return CELLM_ERR_SIZE;
+    if ((sup == nullptr) != (sdown == nullptr) || (sup && (sff < 1 || !smid))) return CELLM_ERR_ARG;
+    if (!sup) sff = 0;
+    const size_t smem_up = (size_t)H * sizeof(float), smem_down = ((size_t)top * ff + sff + 2 * top) * sizeof(float);
     if (smem_up > 200 * 1024 || smem_down > 200 * 1024) return CELLM_ERR_SIZE;
-    const dim3 grid_up((unsigned)(T * top), (unsigned)((ff + EXPERT_ROWS - 1) / EXPERT_ROWS));
+    const int up_rows = ff > sff ? ff : sff;
+    const dim3 grid_up((unsigned)(T * top + (sup ? T : 0)), (unsigned)((up_rows + EXPERT_ROWS - 1) / EXPERT_ROWS));
     const dim3 grid_down((unsigned)T, (unsigned)((H + EXPERT_ROWS - 1) / EXPERT_ROWS));
+    if (grid_up.y > 65535 || grid_down.y > 65535) return CELLM_ERR_SIZE;
 #define GO(TA)                                                                                                                    \
     do {                                                                                                                          \
         static bool configured = false;                                                                                           \
@@ -269,9 +303,10 @@ CELLM_API int cellm_experts_rowwise(void* out, void* mid, const void* y, long lo
             if (e != cudaSuccess) return (int)e;                                                                                  \
             configured = true;                                                                                                    \
         }                                                                                                                         \
-        CELLM_RUN(expert_up_kernel<TA>, grid_up, EXPERT_THREADS, smem_up, stream, (TA*)mid, (const TA*)y, ldy, (const TA*)up, idx, H, ff, top, E, act); \
-        CELLM_RUN(expert_down_kernel<TA>, grid_down, EXPERT_THREADS, smem_down, stream, (TA*)out, (const TA*)mid, (const TA*)down, idx, wts, \
-                  shared, gate, H, ff, top, E);                                                                                   \
+        CELLM_RUN(expert_up_kernel<TA>, grid_up, EXPERT_THREADS, smem_up, stream, (TA*)mid, (TA*)smid, (const TA*)y, ldy, (const TA*)up,  \
+                  (const TA*)sup, idx, T, H, ff, sff, top, E, act);                                                               \
+        CELLM_RUN(expert_down_kernel<TA>, grid_down, EXPERT_THREADS, smem_down, stream, (TA*)out, (const TA*)mid, (const TA*)smid, \
+                  (const TA*)down, (const TA*)sdown, idx, wts, gate, H, ff, sff, top, E);                                         \
     } while (0)
     if (dtype == CELLM_F32) GO(float);
     else if (dtype == CELLM_BF16) GO(__nv_bfloat16);

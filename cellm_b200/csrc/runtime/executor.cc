@@ -61,8 +61,8 @@ typedef int (*AttnPrepFn)(P q, CP qkv, i64 row_stride, CP q_w, CP k_w, int w_tag
                           int hd, int hdv, int hq, int hv, int act_tag, P err, P stream);
 typedef int (*RouteFn)(P idx, P wts, P gate, CP y, i64 ldy, CP router, int w_tag, CP correction, int c_tag, int T, int H, int E, int top,
                        int n_groups, int keep, float scale, int has_gate, int act_tag, P stream);
-typedef int (*ExpertsRowwiseFn)(P out, P mid, CP y, i64 ldy, CP up, CP down, CP idx, CP wts, CP shared, CP gate, int T, int H, int ff, int top,
-                                int E, int act, int tag, P stream);
+typedef int (*ExpertsRowwiseFn)(P out, P mid, P smid, CP y, i64 ldy, CP up, CP down, CP sup, CP sdown, CP idx, CP wts, CP gate, int T, int H,
+                                int ff, int sff, int top, int E, int act, int tag, P stream);
 typedef int (*MoeSortFn)(P row_slot, P slot_row, P tile_group, CP idx, int S, int E, int max_tiles, P stream);
 typedef int (*MoeGatherFn)(P xs, CP y, i64 ldy, CP row_slot, CP tile_group, int rows, int top, int H, P stream);
 typedef int (*MoeCombineFn)(P out, CP Y, CP slot_row, CP wts, CP shared, CP gate, int T, int H, int top, P stream);
@@ -716,6 +716,18 @@ void Run::routed_mlp(const RoutedMlpParams& L, const void* x, void* out) {
                              (int)L.experts, (int)L.top, (int)L.n_groups, (int)L.keep, (float)L.scale, L.shared_gate ? 1 : 0, (int)act,
                              s.stream),
            "route");
+    const bool grouped = act == EXEC_BF16 && T >= p.grouped_min_tokens && tc_ok(L.up, H) && tc_ok(L.down, L.ff) && (((uintptr_t)x) & 15) == 0;
+    if (!grouped) {
+        // few tokens (and 32-bit): every token's chosen experts, and the shared one as one expert more, walked row by row
+        void* mid = arena.take(T * L.top * L.ff * e);
+        void* smid = L.shared_up.w ? arena.take(T * L.shared_ff * e) : nullptr;
+        LAUNCH(fn<ExpertsRowwiseFn>(FN_EXPERTS_ROWWISE)(out, mid, smid, x, H, L.up.w, L.down.w, L.shared_up.w, L.shared_down.w, idx, wts, gate,
+                                                    (int)T, (int)H, (int)L.ff, (int)L.shared_ff, (int)L.top, (int)L.experts, (int)L.act,
+                                                    (int)act, s.stream),
+               "experts_rowwise");
+        ++launches;         // up and down are a launch each
+        return;
+    }
     // the shared expert: two plain products around its activation; its result stays 32-bit until the experts' sum takes it
     void* shared = nullptr;
     if (L.shared_up.w) {
@@ -724,7 +736,7 @@ void Run::routed_mlp(const RoutedMlpParams& L, const void* x, void* out) {
         LAUNCH(fn<ActivationFn>(FN_ACTIVATION)(h, u, L.shared_ff, (int)T, (int)L.shared_ff, (int)L.act, (int)act, s.stream), "activation");
         shared = linear(h, L.shared_down, T, L.shared_ff, EXEC_F32);
     }
-    if (act == EXEC_BF16 && T >= p.grouped_min_tokens && tc_ok(L.up, H) && tc_ok(L.down, L.ff) && (((uintptr_t)x) & 15) == 0) {
+    {
         // many tokens: the slots sorted by expert, every expert's run padded to whole tiles of 128 rows, and the two
         // products as grouped tensor-core products over the sorted rows (the activation in the first one's epilogue)
         const i64 S = T * L.top, rows = ceil_div(S + std::min(L.experts, S) * 127, 128) * 128, tiles = rows / 128;
@@ -743,13 +755,7 @@ void Run::routed_mlp(const RoutedMlpParams& L, const void* x, void* out) {
                                               (int)EXEC_BF16, tile_group, -1, s.err, s.stream),
                "gemm_grouped_tcgen05");
         LAUNCH(fn<MoeCombineFn>(FN_MOE_COMBINE)(out, ys, slot_row, wts, shared, gate, (int)T, (int)H, (int)L.top, s.stream), "moe_combine");
-        return;
     }
-    void* mid = arena.take(T * L.top * L.ff * e);
-    LAUNCH(fn<ExpertsRowwiseFn>(FN_EXPERTS_ROWWISE)(out, mid, x, H, L.up.w, L.down.w, idx, wts, shared, gate, (int)T, (int)H, (int)L.ff,
-                                                (int)L.top, (int)L.experts, (int)L.act, (int)act, s.stream),
-           "experts_rowwise");
-    ++launches;         // up and down are a launch each
 }
 
 void Run::mingru(const MinGruParams& L, const ExecItem& it, const void* x, void* out) {

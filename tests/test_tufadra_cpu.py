@@ -80,7 +80,7 @@ def test_launches_of_a_step(monkeypatch, dtype):
     run_step(model, plan, [5, 1], [0, 7])
     names = rec.names()
     product = "cellm_gemm_tcgen05" if dtype == torch.bfloat16 else "cellm_gemm_plain"
-    experts = ["cellm_route", product, "cellm_activation", product, "cellm_experts_rowwise"]
+    experts = ["cellm_route", "cellm_experts_rowwise"]          # few tokens: the shared expert is walked with the chosen ones
     # portions of at most 16 (token, head) rows a key/value head: the decode kernel, also for the heads padded to 32
     attend = "cellm_attention_decode" if dtype == torch.bfloat16 else "cellm_attention_plain"
     wide = ["cellm_add_rmsnorm", product, "cellm_attn_prep", attend, product]
@@ -152,6 +152,8 @@ def test_many_tokens_take_the_grouped_products(monkeypatch):
     run_step(model, plan, [40, 1], [0, 7])
     names = rec.names()
     assert names.count("cellm_moe_sort") == 2 and names.count("cellm_gemm_grouped_tcgen05") == 4 and "cellm_experts_rowwise" not in names
+    i = names.index("cellm_route")
+    assert names[i:i + 5] == ["cellm_route", "cellm_gemm_tcgen05", "cellm_activation", "cellm_gemm_tcgen05", "cellm_moe_sort"]       # the shared expert
     i = names.index("cellm_moe_sort")
     assert names[i:i + 5] == ["cellm_moe_sort", "cellm_moe_gather", "cellm_gemm_grouped_tcgen05", "cellm_gemm_grouped_tcgen05", "cellm_moe_combine"]
     S, E = 41 * 4, 12
