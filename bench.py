@@ -216,6 +216,7 @@ def profile_region(loaded, args, rng) -> int:
         def step():
             cache.add(counter[0])
             runner.run([StepEntry(counter[0], toks, [n_tok - 1])])
+            cache.release(counter[0])
             counter[0] += 1
     for _ in range(max(args.warmup, 1)):
         step()

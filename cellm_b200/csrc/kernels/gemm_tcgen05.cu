@@ -1019,15 +1019,16 @@ static int gemm_impl(void* C, const void* A, const void* W, int M, int N, int K,
 }
 
 // The grouped product (see the persistent kernel): A [M, K] in tiles of 128 rows, tile i multiplied with matrix
-// tile_group[i] of W [groups * N, K]; C [M, N]. act: -1 none, else an activation on the sums.
+// tile_group[i] of W [groups * N, K]; C [M, N]. act: -1 none, else an activation on the sums. tile_group null (groups = 1):
+// an ordinary product of any M with the activation in its epilogue.
 CELLM_API int cellm_gemm_grouped_tcgen05(void* C, const void* A, const void* W, int M, int N, int K, int groups, long long lda,
                                          long long ldw, long long ldc, int out_dtype, const int* tile_group, int act, int* err,
                                          cudaStream_t stream) {
     if (M <= 0 || N <= 0) return CELLM_OK;
-    if (K <= 0 || (K & 7) || groups < 1 || (M % BM)) return CELLM_ERR_SIZE;
+    if (K <= 0 || (K & 7) || groups < 1 || (tile_group && (M % BM)) || (!tile_group && groups != 1)) return CELLM_ERR_SIZE;
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((lda * 2) & 15) || ((ldw * 2) & 15)) return CELLM_ERR_ALIGN;
     if (out_dtype != CELLM_F32 && out_dtype != CELLM_BF16) return CELLM_ERR_DTYPE;
-    if (!tile_group || act > 3) return CELLM_ERR_ARG;
+    if (act > 3) return CELLM_ERR_ARG;
     const int bn = N > 128 ? 256 : 128;
     CUtensorMap map_a, map_w;
     if (!tensor_map(&map_a, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, (uint32_t)BM)) return CELLM_ERR_ARG;

@@ -12,7 +12,6 @@
 // that depends on the sizes alone, so a token's result does not depend on what else is in the batch.
 #include "common.cuh"
 
-#define ROUTE_THREADS 512
 
 // A lane's share of the dot product of a weight row with a vector held as floats: pieces of 16 bytes where the
 // row allows it (`vec`), else element by element.
@@ -56,180 +55,148 @@ template <typename TW> __device__ __forceinline__ bool rows_vectorise(const TW* 
     return (n % per) == 0 && (ld % per) == 0 && (((uintptr_t)base) & 15) == 0;
 }
 
-// ---- the router ----------------------------------------------------------------------------------------------------
-// One block takes ROUTE_TPB tokens (8, or 1 where eight rows of the input do not fit shared memory): their inputs lie in shared memory, a warp forms one router row's sums for all of
-// them at once, then a warp a token chooses.
-template <int ROUTE_TPB, typename TA, typename TW, typename TC>
-__global__ void __launch_bounds__(ROUTE_THREADS)
-route_kernel(int* __restrict__ idx, float* __restrict__ wts, float* __restrict__ gate_out, const TA* __restrict__ y, long long ldy,
-             const TW* __restrict__ router, const TC* __restrict__ correction, int T, int H, int E, int top, int n_groups, int keep,
-             float scale, int has_gate) {
-    extern __shared__ __align__(16) float smem[];
-    float* hs = smem;                               // [TPB][H]
-    float* sc = hs + (size_t)ROUTE_TPB * H;         // [TPB][E + 1]: logits, then s
-    float* ch = sc + ROUTE_TPB * (E + 1);           // [TPB][E]: choice scores
-    float* gs = ch + ROUTE_TPB * E;                 // [TPB][n_groups]: scores of the runs
-    float* kf = gs + ROUTE_TPB * n_groups;          // [TPB][n_groups]: 1 = the run is kept
-    float* sel = kf + ROUTE_TPB * n_groups;         // [TPB][top]: s of the chosen, by rank
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = ROUTE_THREADS / 32;
-    const int t0 = blockIdx.x * ROUTE_TPB, nt = min(ROUTE_TPB, T - t0);
-    pdl_trigger();
-    pdl_wait();
-    for (int i = threadIdx.x; i < ROUTE_TPB * H; i += ROUTE_THREADS) {
-        const int j = i / H, c = i - j * H;
-        hs[i] = j < nt ? to_float(y[(size_t)(t0 + j) * ldy + c]) : 0.f;
-    }
-    __syncthreads();
-    const int rows = E + (has_gate ? 1 : 0);
-    const bool vec = rows_vectorise(router, H, H);
-    constexpr int PER = 16 / (int)sizeof(TW);       // elements in a 16-byte piece of a router row
-    for (int r = warp; r < rows; r += nwarps) {
-        float acc[ROUTE_TPB];
+// The same for up to four rows at once (row j at w + j * stride; rows >= nrows count as zeros): a[j] += f * (row j . v).
+// The rows' loads are issued together, so a lane has four of them in flight.
+template <typename TW>
+__device__ __forceinline__ void lane_dot4(float (&a)[4], float f, const TW* __restrict__ w, size_t stride, int nrows, const float* __restrict__ v,
+                                          int n, int lane, bool vec) {
+    constexpr int PER = 16 / (int)sizeof(TW);
+    float p[4] = {0.f, 0.f, 0.f, 0.f};
+    if (vec) {
+#pragma unroll 2
+        for (int i = lane * PER; i < n; i += 32 * PER) {
+            uint4 x[4];
 #pragma unroll
-        for (int j = 0; j < ROUTE_TPB; ++j) acc[j] = 0.f;
-        const TW* wr = router + (size_t)r * H;
-        if (vec) {
-            for (int i = lane * PER; i < H; i += 32 * PER) {
-                float w[PER];
-                const uint4 x = *reinterpret_cast<const uint4*>(wr + i);
-                const TW* xp = reinterpret_cast<const TW*>(&x);
+            for (int j = 0; j < 4; ++j) x[j] = j < nrows ? *reinterpret_cast<const uint4*>(w + j * stride + i) : make_uint4(0, 0, 0, 0);
+            float y[PER];
 #pragma unroll
-                for (int k = 0; k < PER; ++k) w[k] = to_float(xp[k]);
-#pragma unroll
-                for (int j = 0; j < ROUTE_TPB; ++j) {
-                    if (j < nt) {
-#pragma unroll
-                        for (int k = 0; k < PER; k += 4) {
-                            const float4 y = *reinterpret_cast<const float4*>(hs + j * H + i + k);
-                            acc[j] += w[k] * y.x + w[k + 1] * y.y + w[k + 2] * y.z + w[k + 3] * y.w;
-                        }
-                    }
-                }
+            for (int k = 0; k < PER; k += 4) {
+                const float4 t = *reinterpret_cast<const float4*>(v + i + k);
+                y[k] = t.x; y[k + 1] = t.y; y[k + 2] = t.z; y[k + 3] = t.w;
             }
-        } else {
-            for (int i = lane; i < H; i += 32) {
-                const float w = to_float(wr[i]);
 #pragma unroll
-                for (int j = 0; j < ROUTE_TPB; ++j) acc[j] += w * hs[j * H + i];
+            for (int j = 0; j < 4; ++j) {
+                const TW* xp = reinterpret_cast<const TW*>(&x[j]);
+#pragma unroll
+                for (int k = 0; k < PER; ++k) p[j] += to_float(xp[k]) * y[k];
             }
         }
+    } else {
+        for (int i = lane; i < n; i += 32) {
+            const float y = v[i];
 #pragma unroll
-        for (int j = 0; j < ROUTE_TPB; ++j) {
-            const float v = warp_sum(acc[j]);
-            if (lane == 0) sc[j * (E + 1) + r] = v;
+            for (int j = 0; j < 4; ++j)
+                if (j < nrows) p[j] += to_float(w[j * stride + i]) * y;
         }
     }
-    __syncthreads();
-    const int gsz = E / n_groups;
-    for (int j = warp; j < nt; j += nwarps) {
-        const int t = t0 + j;
-        float* z = sc + j * (E + 1);
-        float* c = ch + j * E;
-        float* g = gs + j * n_groups;
-        float* k = kf + j * n_groups;
-        float* chosen = sel + j * top;
-        for (int e = lane; e < E; e += 32) {
-            const float s = 1.f / (1.f + expf(-z[e]));
-            z[e] = s;
-            c[e] = s + to_float(correction[e]);
-        }
-        if (has_gate && lane == 0) gate_out[t] = 1.f / (1.f + expf(-z[E]));
-        __syncwarp();
-        if (n_groups > 1) {
-            for (int gi = lane; gi < n_groups; gi += 32) {
-                float m1 = -INFINITY, m2 = -INFINITY;
-                for (int e = gi * gsz; e < (gi + 1) * gsz; ++e) {
-                    const float v = c[e];
-                    if (v > m1) { m2 = m1; m1 = v; }
-                    else if (v > m2) m2 = v;
-                }
-                g[gi] = gsz >= 2 ? m1 + m2 : m1;
-            }
-            __syncwarp();
-            for (int gi = lane; gi < n_groups; gi += 32) {
-                int rank = 0;
-                const float mine = g[gi];
-                for (int gj = 0; gj < n_groups; ++gj) rank += (g[gj] > mine || (g[gj] == mine && gj < gi)) ? 1 : 0;
-                k[gi] = rank < keep ? 1.f : 0.f;
-            }
-            __syncwarp();
-            for (int e = lane; e < E; e += 32)
-                if (k[e / gsz] == 0.f) c[e] = -INFINITY;
-            __syncwarp();
-        }
-        for (int e = lane; e < E; e += 32) {
-            int rank = 0;
-            const float mine = c[e];
-            for (int f = 0; f < E; ++f) rank += (c[f] > mine || (c[f] == mine && f < e)) ? 1 : 0;
-            if (rank < top) {
-                idx[(size_t)t * top + rank] = e;
-                chosen[rank] = z[e];
-            }
-        }
-        __syncwarp();
-        float sum = 0.f;
-        for (int r = 0; r < top; ++r) sum += chosen[r];
-        for (int r = lane; r < top; r += 32) wts[(size_t)t * top + r] = chosen[r] / (sum + 1e-20f) * scale;
-    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) a[j] += f * p[j];
 }
 
-// y: [T, H] (row pitch ldy); router: [E (+1), H], row E the shared expert's gate when has_gate; correction: [E].
-// idx: [T, top] int, wts: [T, top] float, gate_out: [T] float (sigmoid of the gate row's sum).
-CELLM_API int cellm_route(int* idx, float* wts, float* gate_out, const void* y, long long ldy, const void* router, int w_dtype,
-                          const void* correction, int c_dtype, int T, int H, int E, int top, int n_groups, int keep, float scale,
-                          int has_gate, int act_dtype, cudaStream_t stream) {
+// ---- the router ----------------------------------------------------------------------------------------------------
+// The choice from the router's 32-bit sums z [T, E (+1)] (a product's output; column E is the shared expert's gate): a
+// warp a token, its scores in shared memory.
+#define ROUTE_THREADS 128
+
+template <typename TC>
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_kernel(int* __restrict__ idx, float* __restrict__ wts, float* __restrict__ gate_out, const float* __restrict__ z_all, long long ldz,
+             const TC* __restrict__ correction, int T, int E, int top, int n_groups, int keep, float scale, int has_gate) {
+    extern __shared__ __align__(16) float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = ROUTE_THREADS / 32;
+    const int per = 2 * E + 2 * n_groups + top;
+    float* z = smem + (size_t)warp * per;       // [E]: s
+    float* c = z + E;                           // [E]: choice scores
+    float* g = c + E;                           // [n_groups]: scores of the runs
+    float* k = g + n_groups;                    // [n_groups]: 1 = the run is kept
+    float* chosen = k + n_groups;               // [top]: s of the chosen, by rank
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x * nwarps + warp;
+    if (t >= T) return;
+    const float* zr = z_all + (size_t)t * ldz;
+    const int gsz = E / n_groups;
+    for (int e = lane; e < E; e += 32) {
+        const float s = 1.f / (1.f + expf(-zr[e]));
+        z[e] = s;
+        c[e] = s + to_float(correction[e]);
+    }
+    if (has_gate && lane == 0) gate_out[t] = 1.f / (1.f + expf(-zr[E]));
+    __syncwarp();
+    if (n_groups > 1) {
+        for (int gi = lane; gi < n_groups; gi += 32) {
+            float m1 = -INFINITY, m2 = -INFINITY;
+            for (int e = gi * gsz; e < (gi + 1) * gsz; ++e) {
+                const float v = c[e];
+                if (v > m1) { m2 = m1; m1 = v; }
+                else if (v > m2) m2 = v;
+            }
+            g[gi] = gsz >= 2 ? m1 + m2 : m1;
+        }
+        __syncwarp();
+        for (int gi = lane; gi < n_groups; gi += 32) {
+            int rank = 0;
+            const float mine = g[gi];
+            for (int gj = 0; gj < n_groups; ++gj) rank += (g[gj] > mine || (g[gj] == mine && gj < gi)) ? 1 : 0;
+            k[gi] = rank < keep ? 1.f : 0.f;
+        }
+        __syncwarp();
+        for (int e = lane; e < E; e += 32)
+            if (k[e / gsz] == 0.f) c[e] = -INFINITY;
+        __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32) {
+        int rank = 0;
+        const float mine = c[e];
+        for (int f = 0; f < E; ++f) rank += (c[f] > mine || (c[f] == mine && f < e)) ? 1 : 0;
+        if (rank < top) {
+            idx[(size_t)t * top + rank] = e;
+            chosen[rank] = z[e];
+        }
+    }
+    __syncwarp();
+    float sum = 0.f;
+    for (int r = 0; r < top; ++r) sum += chosen[r];
+    for (int r = lane; r < top; r += 32) wts[(size_t)t * top + r] = chosen[r] / (sum + 1e-20f) * scale;
+}
+
+// z: [T, E (+1)] float (row pitch ldz), column E the shared expert's gate when has_gate; correction: [E].
+// idx: [T, top] int, wts: [T, top] float, gate_out: [T] float (sigmoid of the gate column).
+CELLM_API int cellm_route(int* idx, float* wts, float* gate_out, const float* z, long long ldz, const void* correction, int c_dtype, int T,
+                          int E, int top, int n_groups, int keep, float scale, int has_gate, cudaStream_t stream) {
     if (T <= 0) return CELLM_OK;
-    if (E < 1 || top < 1 || top > E || n_groups < 1 || E % n_groups || keep < 1 || keep > n_groups || H < 1) return CELLM_ERR_SIZE;
+    if (E < 1 || top < 1 || top > E || n_groups < 1 || E % n_groups || keep < 1 || keep > n_groups) return CELLM_ERR_SIZE;
     if (has_gate && !gate_out) return CELLM_ERR_ARG;
-    if (w_dtype != act_dtype) return CELLM_ERR_DTYPE;
-    const size_t per_token = ((size_t)H + 2 * E + 1 + 2 * n_groups + top) * sizeof(float);
-    const int tpb = 8 * per_token <= 200 * 1024 ? 8 : 1;
-    const size_t smem = tpb * per_token;
-    if (smem > 200 * 1024) return CELLM_ERR_SIZE;
-    const unsigned blocks = (unsigned)((T + tpb - 1) / tpb);
-#define GO2(TPB, TA, TC)                                                                                                    \
-    do {                                                                                                                    \
-        static size_t configured = 0;                                                                                       \
-        if (smem > 48 * 1024 && smem > configured) {                                                                        \
-            const cudaError_t e = cudaFuncSetAttribute(route_kernel<TPB, TA, TA, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
-            if (e != cudaSuccess) return (int)e;                                                                            \
-            configured = 200 * 1024;                                                                                        \
-        }                                                                                                                   \
-        CELLM_RUN((route_kernel<TPB, TA, TA, TC>), blocks, ROUTE_THREADS, smem, stream, idx, wts, gate_out, (const TA*)y, ldy, \
-                  (const TA*)router, (const TC*)correction, T, H, E, top, n_groups, keep, scale, has_gate);                 \
-    } while (0)
-#define GO(TA, TC)                          \
-    do {                                    \
-        if (tpb == 8) GO2(8, TA, TC);       \
-        else GO2(1, TA, TC);                \
-    } while (0)
-    if (act_dtype == CELLM_F32 && c_dtype == CELLM_F32) GO(float, float);
-    else if (act_dtype == CELLM_F32 && c_dtype == CELLM_BF16) GO(float, __nv_bfloat16);
-    else if (act_dtype == CELLM_BF16 && c_dtype == CELLM_F32) GO(__nv_bfloat16, float);
-    else if (act_dtype == CELLM_BF16 && c_dtype == CELLM_BF16) GO(__nv_bfloat16, __nv_bfloat16);
+    const size_t smem = (size_t)(ROUTE_THREADS / 32) * (2 * E + 2 * n_groups + top) * sizeof(float);
+    if (smem > 48 * 1024) return CELLM_ERR_SIZE;
+    const unsigned blocks = (unsigned)((T + ROUTE_THREADS / 32 - 1) / (ROUTE_THREADS / 32));
+    if (c_dtype == CELLM_F32)
+        CELLM_RUN(route_kernel<float>, blocks, ROUTE_THREADS, smem, stream, idx, wts, gate_out, z, ldz, (const float*)correction, T, E, top,
+                  n_groups, keep, scale, has_gate);
+    else if (c_dtype == CELLM_BF16)
+        CELLM_RUN(route_kernel<__nv_bfloat16>, blocks, ROUTE_THREADS, smem, stream, idx, wts, gate_out, z, ldz, (const __nv_bfloat16*)correction,
+                  T, E, top, n_groups, keep, scale, has_gate);
     else return CELLM_ERR_DTYPE;
-#undef GO2
-#undef GO
     return CELLM_OK;
 }
 
 // ---- the experts, row by row ----------------------------------------------------------------------------------------
 #define EXPERT_THREADS 128
-#define EXPERT_ROWS 4           // output rows a block forms: one a warp
+#define EXPERT_WARPS 4           // a warp forms `rpw` (1, 2 or 4) output rows at once; a block 4 * rpw
 
 // mid[t * top + k, :] = act(U_e y[t]) for e = idx[t, k]; up: [E * ff, H]. Blocks with blockIdx.x >= T * top take the shared
 // expert: smid[t, :] = act(U_s y[t]), U_s: [sff, H].
 template <typename TA>
 __global__ void __launch_bounds__(EXPERT_THREADS)
 expert_up_kernel(TA* __restrict__ mid, TA* __restrict__ smid, const TA* __restrict__ y, long long ldy, const TA* __restrict__ up,
-                 const TA* __restrict__ sup, const int* __restrict__ idx, int T, int H, int ff, int sff, int top, int E, int act) {
+                 const TA* __restrict__ sup, const int* __restrict__ idx, int T, int H, int ff, int sff, int top, int E, int act, int rpw) {
     extern __shared__ __align__(16) float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool is_shared = (int)blockIdx.x >= T * top;
     const int slot = is_shared ? (int)blockIdx.x - T * top : (int)blockIdx.x;
     const int t = is_shared ? slot : slot / top;
     const int rows = is_shared ? sff : ff;
-    if ((int)blockIdx.y * EXPERT_ROWS >= rows) return;
+    if ((int)blockIdx.y * EXPERT_WARPS * rpw >= rows) return;
     const bool vec = rows_vectorise(is_shared ? sup : up, H, H);
     pdl_trigger();
     pdl_wait();
@@ -237,10 +204,14 @@ expert_up_kernel(TA* __restrict__ mid, TA* __restrict__ smid, const TA* __restri
     const TA* base = sup;
     if (!is_shared) base = up + (size_t)min(max(idx[slot], 0), E - 1) * ff * H;
     __syncthreads();
-    const int r = blockIdx.y * EXPERT_ROWS + warp;
-    if (r < rows) {
-        const float d = warp_sum(lane_dot<TA>(base + (size_t)r * H, smem, H, lane, vec));
-        if (lane == 0) (is_shared ? smid : mid)[(size_t)slot * rows + r] = from_float<TA>(cellm_activate(d, act));
+    const int r0 = (blockIdx.y * EXPERT_WARPS + warp) * rpw, nr = min(rpw, rows - r0);
+    if (nr <= 0) return;
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+    lane_dot4<TA>(d, 1.f, base + (size_t)r0 * H, (size_t)H, nr, smem, H, lane, vec);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float v = warp_sum(d[j]);
+        if (lane == 0 && j < nr) (is_shared ? smid : mid)[(size_t)slot * rows + r0 + j] = from_float<TA>(cellm_activate(v, act));
     }
 }
 
@@ -249,7 +220,7 @@ template <typename TA>
 __global__ void __launch_bounds__(EXPERT_THREADS)
 expert_down_kernel(TA* __restrict__ out, const TA* __restrict__ mid, const TA* __restrict__ smid, const TA* __restrict__ down,
                    const TA* __restrict__ sdown, const int* __restrict__ idx, const float* __restrict__ wts, const float* __restrict__ gate,
-                   int H, int ff, int sff, int top, int E) {
+                   int H, int ff, int sff, int top, int E, int rpw) {
     extern __shared__ __align__(16) float smem[];   // [top * ff] the token's middles, [sff] the shared expert's, then [top] weights and experts
     float* ms = smem;
     float* ss = smem + (size_t)top * ff;
@@ -268,14 +239,16 @@ expert_down_kernel(TA* __restrict__ out, const TA* __restrict__ mid, const TA* _
         ek[k] = min(max(idx[(size_t)t * top + k], 0), E - 1);
     }
     __syncthreads();
-    const int r = blockIdx.y * EXPERT_ROWS + warp;
-    if (r < H) {
-        float a = 0.f;
-#pragma unroll 2
-        for (int k = 0; k < top; ++k) a += wk[k] * lane_dot<TA>(down + ((size_t)ek[k] * H + r) * ff, ms + (size_t)k * ff, ff, lane, vec);
-        if (sdown) a += (gate ? gate[t] : 1.f) * lane_dot<TA>(sdown + (size_t)r * sff, ss, sff, lane, svec);
-        a = warp_sum(a);
-        if (lane == 0) out[(size_t)t * H + r] = from_float<TA>(a);
+    const int r0 = (blockIdx.y * EXPERT_WARPS + warp) * rpw, nr = min(rpw, H - r0);
+    if (nr <= 0) return;
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < top; ++k)
+        lane_dot4<TA>(a, wk[k], down + ((size_t)ek[k] * H + r0) * ff, (size_t)ff, nr, ms + (size_t)k * ff, ff, lane, vec);
+    if (sdown) lane_dot4<TA>(a, gate ? gate[t] : 1.f, sdown + (size_t)r0 * sff, (size_t)sff, nr, ss, sff, lane, svec);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float v = warp_sum(a[j]);
+        if (lane == 0 && j < nr) out[(size_t)t * H + r0 + j] = from_float<TA>(v);
     }
 }
 
@@ -291,8 +264,20 @@ CELLM_API int cellm_experts_rowwise(void* out, void* mid, void* smid, const void
     const size_t smem_up = (size_t)H * sizeof(float), smem_down = ((size_t)top * ff + sff + 2 * top) * sizeof(float);
     if (smem_up > 200 * 1024 || smem_down > 200 * 1024) return CELLM_ERR_SIZE;
     const int up_rows = ff > sff ? ff : sff;
-    const dim3 grid_up((unsigned)(T * top + (sup ? T : 0)), (unsigned)((up_rows + EXPERT_ROWS - 1) / EXPERT_ROWS));
-    const dim3 grid_down((unsigned)T, (unsigned)((H + EXPERT_ROWS - 1) / EXPERT_ROWS));
+    // rows a warp: four where that still leaves some 600 blocks (four an SM) at work, else two, else one
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
+    }
+    auto rows_a_warp = [&](long long rows_in_all) {
+        for (int r = 4; r > 1; r /= 2)
+            if (rows_in_all / (EXPERT_WARPS * r) >= 4LL * sms) return r;
+        return 1;
+    };
+    const int rpw_up = rows_a_warp((long long)T * top * ff + (sup ? (long long)T * sff : 0)), rpw_down = rows_a_warp((long long)T * H);
+    const dim3 grid_up((unsigned)(T * top + (sup ? T : 0)), (unsigned)((up_rows + EXPERT_WARPS * rpw_up - 1) / (EXPERT_WARPS * rpw_up)));
+    const dim3 grid_down((unsigned)T, (unsigned)((H + EXPERT_WARPS * rpw_down - 1) / (EXPERT_WARPS * rpw_down)));
     if (grid_up.y > 65535 || grid_down.y > 65535) return CELLM_ERR_SIZE;
 #define GO(TA)                                                                                                                    \
     do {                                                                                                                          \
@@ -304,9 +289,9 @@ CELLM_API int cellm_experts_rowwise(void* out, void* mid, void* smid, const void
             configured = true;                                                                                                    \
         }                                                                                                                         \
         CELLM_RUN(expert_up_kernel<TA>, grid_up, EXPERT_THREADS, smem_up, stream, (TA*)mid, (TA*)smid, (const TA*)y, ldy, (const TA*)up,  \
-                  (const TA*)sup, idx, T, H, ff, sff, top, E, act);                                                               \
+                  (const TA*)sup, idx, T, H, ff, sff, top, E, act, rpw_up);                                                               \
         CELLM_RUN(expert_down_kernel<TA>, grid_down, EXPERT_THREADS, smem_down, stream, (TA*)out, (const TA*)mid, (const TA*)smid, \
-                  (const TA*)down, (const TA*)sdown, idx, wts, gate, H, ff, sff, top, E);                                         \
+                  (const TA*)down, (const TA*)sdown, idx, wts, gate, H, ff, sff, top, E, rpw_down);                                         \
     } while (0)
     if (dtype == CELLM_F32) GO(float);
     else if (dtype == CELLM_BF16) GO(__nv_bfloat16);

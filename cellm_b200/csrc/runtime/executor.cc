@@ -59,8 +59,8 @@ typedef int (*EmbedPosFn)(P out, CP table, int tag, CP ids, CP pos_table, CP pos
 typedef int (*AttnPrepFn)(P q, CP qkv, i64 row_stride, CP q_w, CP k_w, int w_tag, float eps, int span, float temp_coef, int temp_every,
                           CP positions, CP seq, CP bt, int bt_stride, P kp, P vp, int num_pages, int page_size, int T, int nh, int nkv,
                           int hd, int hdv, int hq, int hv, int act_tag, P err, P stream);
-typedef int (*RouteFn)(P idx, P wts, P gate, CP y, i64 ldy, CP router, int w_tag, CP correction, int c_tag, int T, int H, int E, int top,
-                       int n_groups, int keep, float scale, int has_gate, int act_tag, P stream);
+typedef int (*RouteFn)(P idx, P wts, P gate, CP z, i64 ldz, CP correction, int c_tag, int T, int E, int top, int n_groups, int keep, float scale,
+                       int has_gate, P stream);
 typedef int (*ExpertsRowwiseFn)(P out, P mid, P smid, CP y, i64 ldy, CP up, CP down, CP sup, CP sdown, CP idx, CP wts, CP gate, int T, int H,
                                 int ff, int sff, int top, int E, int act, int tag, P stream);
 typedef int (*MoeSortFn)(P row_slot, P slot_row, P tile_group, CP idx, int S, int E, int max_tiles, P stream);
@@ -712,9 +712,10 @@ void Run::routed_mlp(const RoutedMlpParams& L, const void* x, void* out) {
     void* idx = arena.take(T * L.top * 4);
     void* wts = arena.take(T * L.top * 4);
     void* gate = L.shared_gate ? arena.take(T * 4) : nullptr;
-    LAUNCH(fn<RouteFn>(FN_ROUTE)(idx, wts, gate, x, H, L.router.w, (int)L.router.dtype, L.correction, (int)L.c_dtype, (int)T, (int)H,
-                             (int)L.experts, (int)L.top, (int)L.n_groups, (int)L.keep, (float)L.scale, L.shared_gate ? 1 : 0, (int)act,
-                             s.stream),
+    // the router's sums (and the shared expert's gate, one row more of the same matrix) as a product with 32-bit output
+    void* z = linear(x, L.router, T, H, EXEC_F32);
+    LAUNCH(fn<RouteFn>(FN_ROUTE)(idx, wts, gate, z, L.router.N, L.correction, (int)L.c_dtype, (int)T, (int)L.experts, (int)L.top,
+                             (int)L.n_groups, (int)L.keep, (float)L.scale, L.shared_gate ? 1 : 0, s.stream),
            "route");
     const bool grouped = act == EXEC_BF16 && T >= p.grouped_min_tokens && tc_ok(L.up, H) && tc_ok(L.down, L.ff) && (((uintptr_t)x) & 15) == 0;
     if (!grouped) {
@@ -731,9 +732,15 @@ void Run::routed_mlp(const RoutedMlpParams& L, const void* x, void* out) {
     // the shared expert: two plain products around its activation; its result stays 32-bit until the experts' sum takes it
     void* shared = nullptr;
     if (L.shared_up.w) {
-        void* u = linear(x, L.shared_up, T, H, EXEC_F32);
         void* h = arena.take(T * L.shared_ff * e);
-        LAUNCH(fn<ActivationFn>(FN_ACTIVATION)(h, u, L.shared_ff, (int)T, (int)L.shared_ff, (int)L.act, (int)act, s.stream), "activation");
+        if (tc_ok(L.shared_up, H)) {        // the activation on the 32-bit sums in the product's epilogue
+            LAUNCH(fn<GemmGroupedFn>(FN_GEMM_GROUPED)(h, x, L.shared_up.w, (int)T, (int)L.shared_ff, (int)H, 1, H, L.shared_up.ldw, L.shared_ff,
+                                                  (int)EXEC_BF16, nullptr, (int)L.act, s.err, s.stream),
+                   "gemm_grouped_tcgen05");
+        } else {
+            void* u = linear(x, L.shared_up, T, H, EXEC_F32);
+            LAUNCH(fn<ActivationFn>(FN_ACTIVATION)(h, u, L.shared_ff, (int)T, (int)L.shared_ff, (int)L.act, (int)act, s.stream), "activation");
+        }
         shared = linear(h, L.shared_down, T, L.shared_ff, EXEC_F32);
     }
     {

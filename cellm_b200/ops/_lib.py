@@ -37,7 +37,7 @@ _SIGNATURES = {
         "cellm_bias_add": [P, P, P, I, I, I, I, P],
         "cellm_attn_prep": [P, P, L, P, P, I, F, I, F, I, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, I, P, P],
         "cellm_attention_plain_wide": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P],
-        "cellm_route": [P, P, P, P, L, P, I, P, I, I, I, I, I, I, I, F, I, I, P],
+        "cellm_route": [P, P, P, P, L, P, I, I, I, I, I, I, F, I, P],
         "cellm_experts_rowwise": [P, P, P, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
         "cellm_activation": [P, P, L, I, I, I, I, P],
         "cellm_moe_sort": [P, P, P, P, I, I, I, P],

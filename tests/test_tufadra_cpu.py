@@ -80,7 +80,7 @@ def test_launches_of_a_step(monkeypatch, dtype):
     run_step(model, plan, [5, 1], [0, 7])
     names = rec.names()
     product = "cellm_gemm_tcgen05" if dtype == torch.bfloat16 else "cellm_gemm_plain"
-    experts = ["cellm_route", "cellm_experts_rowwise"]          # few tokens: the shared expert is walked with the chosen ones
+    experts = [product, "cellm_route", "cellm_experts_rowwise"]          # few tokens: the shared expert is walked with the chosen ones
     # portions of at most 16 (token, head) rows a key/value head: the decode kernel, also for the heads padded to 32
     attend = "cellm_attention_decode" if dtype == torch.bfloat16 else "cellm_attention_plain"
     wide = ["cellm_add_rmsnorm", product, "cellm_attn_prep", attend, product]
@@ -96,7 +96,7 @@ def test_launches_of_a_step(monkeypatch, dtype):
     out_proj = rec.of(product)[1]
     assert out_proj[5] == 6 * 32           # K of the output product: the padded heads
     route = rec.of("cellm_route")[0]
-    assert route[9:15] == (6, 96, 12, 4, 3, 2) and route[16] == 1
+    assert route[4] == 13 and route[7:12] == (6, 12, 4, 3, 2) and route[13] == 1       # 12 router rows and the gate's
 
 
 def test_decoded_tokens_of_equal_widths_take_the_decode_kernel(monkeypatch):
@@ -151,16 +151,18 @@ def test_many_tokens_take_the_grouped_products(monkeypatch):
     cfg, plan, model = zero_model(copy.deepcopy(CONFIG), torch.bfloat16)
     run_step(model, plan, [40, 1], [0, 7])
     names = rec.names()
-    assert names.count("cellm_moe_sort") == 2 and names.count("cellm_gemm_grouped_tcgen05") == 4 and "cellm_experts_rowwise" not in names
+    assert names.count("cellm_moe_sort") == 2 and names.count("cellm_gemm_grouped_tcgen05") == 6 and "cellm_experts_rowwise" not in names
     i = names.index("cellm_route")
-    assert names[i:i + 5] == ["cellm_route", "cellm_gemm_tcgen05", "cellm_activation", "cellm_gemm_tcgen05", "cellm_moe_sort"]       # the shared expert
+    assert names[i - 1:i + 4] == ["cellm_gemm_tcgen05", "cellm_route", "cellm_gemm_grouped_tcgen05", "cellm_gemm_tcgen05",
+                                  "cellm_moe_sort"]       # the router's sums, the choice, the shared expert (gelu in its first product)
     i = names.index("cellm_moe_sort")
     assert names[i:i + 5] == ["cellm_moe_sort", "cellm_moe_gather", "cellm_gemm_grouped_tcgen05", "cellm_gemm_grouped_tcgen05", "cellm_moe_combine"]
     S, E = 41 * 4, 12
     rows = -(-(S + E * 127) // 128) * 128
     sort = rec.of("cellm_moe_sort")[0]
     assert sort[4:7] == (S, E, rows // 128)
-    up, down = rec.of("cellm_gemm_grouped_tcgen05")[:2]
+    shared_up, up, down = rec.of("cellm_gemm_grouped_tcgen05")[:3]
+    assert shared_up[3:7] == (41, 56, 96, 1) and shared_up[11] is None and shared_up[12] == 0
     assert up[3:7] == (rows, 40, 96, 12) and up[12] == 0            # the exact gelu in the first product's epilogue
     assert down[3:7] == (rows, 96, 40, 12) and down[12] == -1
     rec2 = Recorder(monkeypatch)

@@ -378,11 +378,12 @@ def test_route_choice_and_weights():
         correction[1] = correction[0]
         idx = torch.empty(T, top, dtype=torch.int32, device=DEV)
         wts = torch.empty(T, top, device=DEV)
-        xd, rd, cd = x.to(DEV), router.to(DEV), correction.to(DEV)
-        rc = fn("kernels_common", "cellm_route")(ptr(idx), ptr(wts), None, ptr(xd), H, ptr(rd), tag(rd), ptr(cd), tag(cd), T, H, E, top,
-                                                  groups, keep, 2.5, 0, tag(xd), stream_of(xd))
+        z = (x @ router.T).contiguous()
+        zd, cd = z.to(DEV), correction.to(DEV)
+        rc = fn("kernels_common", "cellm_route")(ptr(idx), ptr(wts), None, ptr(zd), E, ptr(cd), tag(cd), T, E, top, groups, keep, 2.5, 0,
+                                                  stream_of(zd))
         assert rc == 0
-        want_idx, want_w = plain.route(x.double() @ router.double().T, correction.double(), top, {"count": groups, "keep": keep}, 2.5)
+        want_idx, want_w = plain.route(z.double(), correction.double(), top, {"count": groups, "keep": keep}, 2.5)
         assert torch.equal(idx.cpu().long(), want_idx), (E, top, groups, keep)
         torch.testing.assert_close(wts.cpu().double(), want_w, rtol=1e-5, atol=1e-6)
 
