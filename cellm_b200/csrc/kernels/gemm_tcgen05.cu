@@ -709,9 +709,12 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             bool waited = false;
             if (!w_is_static || tile_group) { pdl_wait(); waited = true; }     // the tiles' groups are an earlier kernel's work
             for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
-                const int grp = tile_group ? tile_group[tile % m_tiles] : 0;
+                // grouped: the column tiles of one row tile run side by side (they share the tile of A, and the row tiles of one
+                // matrix of W follow each other), else the row tiles of one column tile
+                const int mt = tile_group ? tile / n_tiles : tile % m_tiles, nt = tile_group ? tile % n_tiles : tile / m_tiles;
+                const int grp = tile_group ? tile_group[mt] : 0;
                 if (grp < 0) continue;
-                const int p0 = (tile % m_tiles) * BM, q0 = (tile / m_tiles) * bn + grp * N;
+                const int p0 = mt * BM, q0 = nt * bn + grp * N;
                 int kb = 0;
                 if (!waited) {
                     // static weights: the ring's first loads of W go out before the wait on the preceding kernel
@@ -742,7 +745,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             int it = 0, tcount = 0;
             if (tile_group) pdl_wait();
             for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
-                if (tile_group && tile_group[tile % m_tiles] < 0) continue;
+                if (tile_group && tile_group[tile / n_tiles] < 0) continue;
                 const int buf = tcount & 1;
                 const uint32_t acc_phase = (uint32_t)(tcount >> 1) & 1u;
                 if (!mbar_wait(&sm.acc_empty2[buf], acc_phase ^ 1u, abort_flag)) { *abort_flag = 1; atomicOr(err, CELLM_DEV_WAIT_TIMEOUT); break; }
@@ -773,7 +776,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         int tcount = 0;
         if (tile_group) { pdl_wait(); waited = true; }
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-            if (tile_group && tile_group[tile % m_tiles] < 0) continue;
+            if (tile_group && tile_group[tile / n_tiles] < 0) continue;
             const int buf = tcount & 1;
             const uint32_t acc_phase = (uint32_t)(tcount >> 1) & 1u;
             if (!mbar_wait(&sm.acc_full2[buf], acc_phase, abort_flag)) {
@@ -782,7 +785,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             }
             tc_fence_after();
             if (!waited) { pdl_wait(); waited = true; }    // stores must not pass the kernel before this one
-            const int p0 = (tile % m_tiles) * BM, q0 = (tile / m_tiles) * bn;
+            const int p0 = (tile_group ? tile / n_tiles : tile % m_tiles) * BM, q0 = (tile_group ? tile % n_tiles : tile / m_tiles) * bn;
             const int p = p0 + pl;
             const uint32_t lane_addr = tmem + ((uint32_t)(qtr * 32) << 16) + (uint32_t)(buf * BN);
             if constexpr (EPI == 0) {

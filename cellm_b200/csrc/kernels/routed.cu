@@ -182,7 +182,8 @@ CELLM_API int cellm_route(int* idx, float* wts, float* gate_out, const float* z,
 
 // ---- the experts, row by row ----------------------------------------------------------------------------------------
 #define EXPERT_THREADS 128
-#define EXPERT_WARPS 4           // a warp forms `rpw` (1, 2 or 4) output rows at once; a block 4 * rpw
+#define EXPERT_WARPS 4           // a warp forms `rpw` (1, 2 or 4) output rows at once; a block of the first kernel 4 * rpw
+#define EXPERT_DOWN_WARPS 8      // the second kernel's blocks hold a token's middles in shared memory: more warps share them
 
 // mid[t * top + k, :] = act(U_e y[t]) for e = idx[t, k]; up: [E * ff, H]. Blocks with blockIdx.x >= T * top take the shared
 // expert: smid[t, :] = act(U_s y[t]), U_s: [sff, H].
@@ -217,7 +218,7 @@ expert_up_kernel(TA* __restrict__ mid, TA* __restrict__ smid, const TA* __restri
 
 // out[t, r] = sum_k wts[t, k] * (D_e mid[t * top + k])[r] (+ gate[t] * (D_s smid[t])[r]); down: [E * H, ff], D_s: [H, sff]
 template <typename TA>
-__global__ void __launch_bounds__(EXPERT_THREADS)
+__global__ void __launch_bounds__(EXPERT_DOWN_WARPS * 32)
 expert_down_kernel(TA* __restrict__ out, const TA* __restrict__ mid, const TA* __restrict__ smid, const TA* __restrict__ down,
                    const TA* __restrict__ sdown, const int* __restrict__ idx, const float* __restrict__ wts, const float* __restrict__ gate,
                    int H, int ff, int sff, int top, int E, int rpw) {
@@ -231,15 +232,15 @@ expert_down_kernel(TA* __restrict__ out, const TA* __restrict__ mid, const TA* _
     const bool vec = rows_vectorise(down, ff, ff) && (ff & 3) == 0, svec = sdown && rows_vectorise(sdown, sff, sff) && ((top * ff) & 3) == 0;
     pdl_trigger();
     pdl_wait();
-    for (int i = threadIdx.x; i < top * ff; i += EXPERT_THREADS) ms[i] = to_float(mid[(size_t)t * top * ff + i]);
+    for (int i = threadIdx.x; i < top * ff; i += EXPERT_DOWN_WARPS * 32) ms[i] = to_float(mid[(size_t)t * top * ff + i]);
     if (sdown)
-        for (int i = threadIdx.x; i < sff; i += EXPERT_THREADS) ss[i] = to_float(smid[(size_t)t * sff + i]);
-    for (int k = threadIdx.x; k < top; k += EXPERT_THREADS) {
+        for (int i = threadIdx.x; i < sff; i += EXPERT_DOWN_WARPS * 32) ss[i] = to_float(smid[(size_t)t * sff + i]);
+    for (int k = threadIdx.x; k < top; k += EXPERT_DOWN_WARPS * 32) {
         wk[k] = wts[(size_t)t * top + k];
         ek[k] = min(max(idx[(size_t)t * top + k], 0), E - 1);
     }
     __syncthreads();
-    const int r0 = (blockIdx.y * EXPERT_WARPS + warp) * rpw, nr = min(rpw, H - r0);
+    const int r0 = (blockIdx.y * EXPERT_DOWN_WARPS + warp) * rpw, nr = min(rpw, H - r0);
     if (nr <= 0) return;
     float a[4] = {0.f, 0.f, 0.f, 0.f};
     for (int k = 0; k < top; ++k)
@@ -275,9 +276,12 @@ CELLM_API int cellm_experts_rowwise(void* out, void* mid, void* smid, const void
             if (rows_in_all / (EXPERT_WARPS * r) >= 4LL * sms) return r;
         return 1;
     };
-    const int rpw_up = rows_a_warp((long long)T * top * ff + (sup ? (long long)T * sff : 0)), rpw_down = rows_a_warp((long long)T * H);
+    const int rpw_up = rows_a_warp((long long)T * top * ff + (sup ? (long long)T * sff : 0));
+    int rpw_down = 1;
+    for (int r = 4; r > 1; r /= 2)
+        if ((long long)T * H / (EXPERT_DOWN_WARPS * r) >= 2LL * sms) { rpw_down = r; break; }
     const dim3 grid_up((unsigned)(T * top + (sup ? T : 0)), (unsigned)((up_rows + EXPERT_WARPS * rpw_up - 1) / (EXPERT_WARPS * rpw_up)));
-    const dim3 grid_down((unsigned)T, (unsigned)((H + EXPERT_WARPS * rpw_down - 1) / (EXPERT_WARPS * rpw_down)));
+    const dim3 grid_down((unsigned)T, (unsigned)((H + EXPERT_DOWN_WARPS * rpw_down - 1) / (EXPERT_DOWN_WARPS * rpw_down)));
     if (grid_up.y > 65535 || grid_down.y > 65535) return CELLM_ERR_SIZE;
 #define GO(TA)                                                                                                                    \
     do {                                                                                                                          \
@@ -290,7 +294,7 @@ CELLM_API int cellm_experts_rowwise(void* out, void* mid, void* smid, const void
         }                                                                                                                         \
         CELLM_RUN(expert_up_kernel<TA>, grid_up, EXPERT_THREADS, smem_up, stream, (TA*)mid, (TA*)smid, (const TA*)y, ldy, (const TA*)up,  \
                   (const TA*)sup, idx, T, H, ff, sff, top, E, act, rpw_up);                                                               \
-        CELLM_RUN(expert_down_kernel<TA>, grid_down, EXPERT_THREADS, smem_down, stream, (TA*)out, (const TA*)mid, (const TA*)smid, \
+        CELLM_RUN(expert_down_kernel<TA>, grid_down, EXPERT_DOWN_WARPS * 32, smem_down, stream, (TA*)out, (const TA*)mid, (const TA*)smid, \
                   (const TA*)down, (const TA*)sdown, idx, wts, gate, H, ff, sff, top, E, rpw_down);                                         \
     } while (0)
     if (dtype == CELLM_F32) GO(float);
