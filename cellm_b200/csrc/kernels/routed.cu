@@ -93,6 +93,47 @@ __device__ __forceinline__ void lane_dot4(float (&a)[4], float f, const TW* __re
     for (int j = 0; j < 4; ++j) a[j] += f * p[j];
 }
 
+// One output row of up to four experts at once (expert j: row w[j] against its own vector v[j], factor f[j]): the sum of
+// f[j] * (w[j] . v[j]) in the order of j, a lane's share. The experts' loads are issued together.
+template <typename TW>
+__device__ __forceinline__ float lane_dot_experts(const TW* const (&w)[4], const float* const (&v)[4], const float (&f)[4], int count, int n, int lane,
+                                                  bool vec) {
+    constexpr int PER = 16 / (int)sizeof(TW);
+    float p[4] = {0.f, 0.f, 0.f, 0.f};
+    if (vec) {
+#pragma unroll 2
+        for (int i = lane * PER; i < n; i += 32 * PER) {
+            uint4 x[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) x[j] = j < count ? *reinterpret_cast<const uint4*>(w[j] + i) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (j < count) {
+                    const TW* xp = reinterpret_cast<const TW*>(&x[j]);
+#pragma unroll
+                    for (int k = 0; k < PER; k += 4) {
+                        const float4 t = *reinterpret_cast<const float4*>(v[j] + i + k);
+                        p[j] += to_float(xp[k]) * t.x;
+                        p[j] += to_float(xp[k + 1]) * t.y;
+                        p[j] += to_float(xp[k + 2]) * t.z;
+                        p[j] += to_float(xp[k + 3]) * t.w;
+                    }
+                }
+            }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (j < count) p[j] += to_float(w[j][i]) * v[j][i];
+    }
+    float a = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if (j < count) a += f[j] * p[j];
+    return a;
+}
+
 // ---- the router ----------------------------------------------------------------------------------------------------
 // The choice from the router's 32-bit sums z [T, E (+1)] (a product's output; column E is the shared expert's gate): a
 // warp a token, its scores in shared memory.
@@ -243,8 +284,24 @@ expert_down_kernel(TA* __restrict__ out, const TA* __restrict__ mid, const TA* _
     const int r0 = (blockIdx.y * EXPERT_DOWN_WARPS + warp) * rpw, nr = min(rpw, H - r0);
     if (nr <= 0) return;
     float a[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int k = 0; k < top; ++k)
-        lane_dot4<TA>(a, wk[k], down + ((size_t)ek[k] * H + r0) * ff, (size_t)ff, nr, ms + (size_t)k * ff, ff, lane, vec);
+    if (rpw == 1) {     // few tokens: one row a warp, four experts' rows in flight at once
+        for (int k0 = 0; k0 < top; k0 += 4) {
+            const TA* w[4];
+            const float* v[4];
+            float f[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int k = min(k0 + j, top - 1);
+                w[j] = down + ((size_t)ek[k] * H + r0) * ff;
+                v[j] = ms + (size_t)k * ff;
+                f[j] = wk[k];
+            }
+            a[0] += lane_dot_experts<TA>(w, v, f, min(4, top - k0), ff, lane, vec);
+        }
+    } else {
+        for (int k = 0; k < top; ++k)
+            lane_dot4<TA>(a, wk[k], down + ((size_t)ek[k] * H + r0) * ff, (size_t)ff, nr, ms + (size_t)k * ff, ff, lane, vec);
+    }
     if (sdown) lane_dot4<TA>(a, gate ? gate[t] : 1.f, sdown + (size_t)r0 * sff, (size_t)sff, nr, ss, sff, lane, svec);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
