@@ -1,6 +1,7 @@
-// Routed feed-forward ("mixture of experts"): the router with its choice of experts, and the experts' two
-// products in the form that serves few tokens and the 32-bit path (a token's chosen experts are walked row by
-// row; every weight row a token needs is read once for it).
+// Routed feed-forward ("mixture of experts"): the choice of experts from the router's sums (which a product forms),
+// the experts' two products in the form that serves few tokens and the 32-bit path (a token's chosen experts, and the
+// shared expert, walked row by row), and for many tokens the sort of the (token, choice) slots by expert, the gather
+// of their rows and the weighted sum of the results around the grouped tensor-core products (gemm_tcgen05.cu).
 //
 //   z = R h (32-bit sums);  s = sigmoid(z);  c = s + correction          (c chooses, s weighs)
 //   experts lie in `n_groups` equal runs of neighbours; a run's score is the sum of its two largest c (its
@@ -13,50 +14,15 @@
 #include "common.cuh"
 
 
-// A lane's share of the dot product of a weight row with a vector held as floats: pieces of 16 bytes where the
-// row allows it (`vec`), else element by element.
-template <typename TW>
-__device__ __forceinline__ float lane_dot(const TW* __restrict__ w, const float* __restrict__ v, int n, int lane, bool vec);
-template <>
-__device__ __forceinline__ float lane_dot<float>(const float* __restrict__ w, const float* __restrict__ v, int n, int lane, bool vec) {
-    float a = 0.f;
-    if (vec) {
-#pragma unroll 4
-        for (int i = lane * 4; i < n; i += 128) {
-            const float4 x = *reinterpret_cast<const float4*>(w + i);
-            const float4 y = *reinterpret_cast<const float4*>(v + i);
-            a += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
-        }
-    } else {
-        for (int i = lane; i < n; i += 32) a += w[i] * v[i];
-    }
-    return a;
-}
-template <>
-__device__ __forceinline__ float lane_dot<__nv_bfloat16>(const __nv_bfloat16* __restrict__ w, const float* __restrict__ v, int n, int lane,
-                                                        bool vec) {
-    float a = 0.f;
-    if (vec) {
-#pragma unroll 4
-        for (int i = lane * 8; i < n; i += 256) {
-            const uint4 x = *reinterpret_cast<const uint4*>(w + i);
-            const float4 y0 = *reinterpret_cast<const float4*>(v + i), y1 = *reinterpret_cast<const float4*>(v + i + 4);
-            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&x);
-            const float2 f0 = __bfloat1622float2(p[0]), f1 = __bfloat1622float2(p[1]), f2 = __bfloat1622float2(p[2]), f3 = __bfloat1622float2(p[3]);
-            a += f0.x * y0.x + f0.y * y0.y + f1.x * y0.z + f1.y * y0.w + f2.x * y1.x + f2.y * y1.y + f3.x * y1.z + f3.y * y1.w;
-        }
-    } else {
-        for (int i = lane; i < n; i += 32) a += __bfloat162float(w[i]) * v[i];
-    }
-    return a;
-}
+// Whether rows of n values (pitch ld) can be read in pieces of 16 bytes.
 template <typename TW> __device__ __forceinline__ bool rows_vectorise(const TW* base, long long ld, int n) {
     constexpr int per = 16 / (int)sizeof(TW);
     return (n % per) == 0 && (ld % per) == 0 && (((uintptr_t)base) & 15) == 0;
 }
 
-// The same for up to four rows at once (row j at w + j * stride; rows >= nrows count as zeros): a[j] += f * (row j . v).
-// The rows' loads are issued together, so a lane has four of them in flight.
+// A lane's share of the dot products of up to four weight rows (row j at w + j * stride; rows >= nrows count as zeros)
+// with a vector held as floats, in pieces of 16 bytes where the rows allow it (`vec`), else element by element:
+// a[j] += f * (row j . v). The rows' loads are issued together, so a lane has four of them in flight.
 template <typename TW>
 __device__ __forceinline__ void lane_dot4(float (&a)[4], float f, const TW* __restrict__ w, size_t stride, int nrows, const float* __restrict__ v,
                                           int n, int lane, bool vec) {
