@@ -325,6 +325,7 @@ def _ctx(T, dtype):
 ROUTED = [  # H, experts, top, ff, groups, keep, shared_ff
     (96, 12, 4, 40, 3, 2, 56), (54, 5, 4, 21, 1, 1, 33), (128, 16, 1, 64, 16, 5, 0), (64, 8, 8, 32, 2, 2, 16),
     (2048, 64, 6, 256, 8, 4, 512), (100, 6, 2, 24, 3, 3, 8), (256, 32, 3, 128, 4, 1, 0),
+    (64, 4, 4, 4096, 1, 1, 0),          # a token's middles beyond 48 KB of shared memory in the second row-by-row kernel
 ]
 
 
