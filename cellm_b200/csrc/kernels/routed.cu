@@ -208,7 +208,20 @@ expert_up_kernel(TA* __restrict__ mid, TA* __restrict__ smid, const TA* __restri
     const bool vec = rows_vectorise(is_shared ? sup : up, H, H);
     pdl_trigger();
     pdl_wait();
-    for (int i = threadIdx.x; i < H; i += EXPERT_THREADS) smem[i] = to_float(y[(size_t)t * ldy + i]);
+    {   // the token's input into shared memory as floats, in 16-byte pieces where its row allows it
+        constexpr int PER = 16 / (int)sizeof(TA);
+        const TA* src = y + (size_t)t * ldy;
+        if (H % PER == 0 && (((uintptr_t)src) & 15) == 0) {
+            for (int i = threadIdx.x * PER; i < H; i += EXPERT_THREADS * PER) {
+                const uint4 x = *reinterpret_cast<const uint4*>(src + i);
+                const TA* xp = reinterpret_cast<const TA*>(&x);
+#pragma unroll
+                for (int k = 0; k < PER; ++k) smem[i + k] = to_float(xp[k]);
+            }
+        } else {
+            for (int i = threadIdx.x; i < H; i += EXPERT_THREADS) smem[i] = to_float(src[i]);
+        }
+    }
     const TA* base = sup;
     if (!is_shared) base = up + (size_t)min(max(idx[slot], 0), E - 1) * ff * H;
     __syncthreads();
@@ -239,9 +252,34 @@ expert_down_kernel(TA* __restrict__ out, const TA* __restrict__ mid, const TA* _
     const bool vec = rows_vectorise(down, ff, ff) && (ff & 3) == 0, svec = sdown && rows_vectorise(sdown, sff, sff) && ((top * ff) & 3) == 0;
     pdl_trigger();
     pdl_wait();
-    for (int i = threadIdx.x; i < top * ff; i += EXPERT_DOWN_WARPS * 32) ms[i] = to_float(mid[(size_t)t * top * ff + i]);
-    if (sdown)
-        for (int i = threadIdx.x; i < sff; i += EXPERT_DOWN_WARPS * 32) ss[i] = to_float(smid[(size_t)t * sff + i]);
+    {   // the token's middles into shared memory as floats, in 16-byte pieces where their rows allow it
+        constexpr int PER = 16 / (int)sizeof(TA);
+        const TA* src = mid + (size_t)t * top * ff;
+        const int n = top * ff;
+        if (n % PER == 0 && (((uintptr_t)src) & 15) == 0) {
+            for (int i = threadIdx.x * PER; i < n; i += EXPERT_DOWN_WARPS * 32 * PER) {
+                const uint4 x = *reinterpret_cast<const uint4*>(src + i);
+                const TA* xp = reinterpret_cast<const TA*>(&x);
+#pragma unroll
+                for (int k = 0; k < PER; ++k) ms[i + k] = to_float(xp[k]);
+            }
+        } else {
+            for (int i = threadIdx.x; i < n; i += EXPERT_DOWN_WARPS * 32) ms[i] = to_float(src[i]);
+        }
+        if (sdown) {
+            const TA* ssrc = smid + (size_t)t * sff;
+            if (sff % PER == 0 && (((uintptr_t)ssrc) & 15) == 0) {
+                for (int i = threadIdx.x * PER; i < sff; i += EXPERT_DOWN_WARPS * 32 * PER) {
+                    const uint4 x = *reinterpret_cast<const uint4*>(ssrc + i);
+                    const TA* xp = reinterpret_cast<const TA*>(&x);
+#pragma unroll
+                    for (int k = 0; k < PER; ++k) ss[i + k] = to_float(xp[k]);
+                }
+            } else {
+                for (int i = threadIdx.x; i < sff; i += EXPERT_DOWN_WARPS * 32) ss[i] = to_float(ssrc[i]);
+            }
+        }
+    }
     for (int k = threadIdx.x; k < top; k += EXPERT_DOWN_WARPS * 32) {
         wk[k] = wts[(size_t)t * top + k];
         ek[k] = min(max(idx[(size_t)t * top + k], 0), E - 1);
