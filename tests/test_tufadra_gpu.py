@@ -432,14 +432,16 @@ def test_embedding_with_learned_positions():
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("which", ["attention alone", "with experts", "one head, wide values", "equal widths", "wider than any fast kernel",
-                                   "equal and odd"])
+                                   "equal and odd", "five query heads a key head", "seven", "twelve", "sixteen"])
 def test_one_layer_alone(tmp_path, dtype, which):
     lay = {"attention alone": layer(attn(4, 2, 16, 24, q_temp=(0.5, 8))),
            "with experts": layer(attn(2, 2, 8, 8), moe(24, 6, 2, 1.5, groups=(3, 2), shared=16)),
            "one head, wide values": layer(attn(1, 1, 16, 48, q_temp=(2.0, 3))),
            "equal widths": layer(attn(4, 1, 32, 32)),
            "wider than any fast kernel": layer(attn(2, 1, 136, 40, q_temp=(0.5, 8))),      # values in rows of their own width
-           "equal and odd": layer(attn(3, 3, 20, 20))}[which]
+           "equal and odd": layer(attn(3, 3, 20, 20)),
+           "five query heads a key head": layer(attn(10, 2, 32, 32, q_temp=(0.3, 16))), "seven": layer(attn(7, 1, 64, 64)),
+           "twelve": layer(attn(12, 1, 16, 24)), "sixteen": layer(attn(32, 2, 8, 8))}[which]
     config = model_config(97, 48, 64, 1e-5, [lay])
     folder = write_model(tmp_path / "one", config, 9)
     if dtype == "bfloat16":
